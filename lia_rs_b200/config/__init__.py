@@ -1,7 +1,8 @@
 from .model_config import ConfigError, LlamaConfig, read_config_json
 from .nafevik_config import NafevikConfig
 from .vatunex_config import VatunexConfig
+from .zipelix_config import ZipelixConfig
 from .registry import Architecture, known_architectures, register_architecture, resolve_architecture
 
-__all__ = ["ConfigError", "LlamaConfig", "NafevikConfig", "VatunexConfig", "read_config_json", "Architecture",
+__all__ = ["ConfigError", "LlamaConfig", "NafevikConfig", "VatunexConfig", "ZipelixConfig", "read_config_json", "Architecture",
            "known_architectures", "register_architecture", "resolve_architecture"]

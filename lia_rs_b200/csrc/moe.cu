@@ -1,0 +1,276 @@
+// A mixture of gated feed-forward experts: each token goes to the `top` experts with the largest router scores.
+//
+//  * `moe_route`: z = W_router x in 32-bit (W_router 32-bit, x in the compute element type), s = softmax(z) over all
+//    experts, the `top` largest s chosen (the lower index wins a tie), their weights s_e * scale (not renormalised);
+//    an optional extra row of the router matrix gives one more logit a token, whose logistic function is the gate of a
+//    shared expert.
+//  * `moe_plan`: the (token, choice) pairs grouped by expert: where each expert's rows begin, which pair each sorted row
+//    is, where each pair went, and the list of (expert, first row) tiles of TILE_M rows that the products run over.
+//    Which pair gets which row inside an expert's group is not fixed, and does not matter: every row of a product is
+//    computed for itself, its sum over K in ascending order.
+//  * `moe_gemm`: for every tile, rows x W_e^T with the expert's own matrix: `MODE_GATE_UP` reads token rows through the
+//    sorted list and writes up * silu(gate) of [W_gate; W_up]; `MODE_DOWN` reads the sorted rows and writes 32-bit rows.
+//  * `moe_combine`: residual (+)= alpha * (sum_c weight_c y[row of (t, c)] + gate_t shared_t), the choices added in
+//    their order, so a token's result does not depend on what else is in the batch.
+#include "common.cuh"
+
+namespace {
+constexpr int TILE_M = 32, TILE_N = 64, TILE_K = 32;
+constexpr int MOE_MAX_EXPERTS = 1024, MOE_MAX_TOP = 32;
+
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ x, long long ld, const float* __restrict__ router, int hidden,
+                                 int experts, int top, float scale, int extra, int* __restrict__ ids,
+                                 float* __restrict__ weights, float* __restrict__ shared_gate) {
+    extern __shared__ float route_shared[];               // x [hidden], z [experts + extra]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    float* xs = route_shared;
+    float* z = xs + hidden;
+    const T* row = x + (size_t)t * ld;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = to_float(row[i]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int e = warp; e < experts + extra; e += warps) {
+        const float* w = router + (size_t)e * hidden;
+        float acc = 0.f;
+        for (int i = lane; i < hidden; i += 32) acc = fmaf(xs[i], w[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) z[e] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    float largest = -INFINITY;
+    for (int e = 0; e < experts; ++e) largest = fmaxf(largest, z[e]);
+    float total = 0.f;
+    for (int e = 0; e < experts; ++e) {
+        z[e] = expf(z[e] - largest);
+        total += z[e];
+    }
+    const float inv = 1.0f / total;
+    for (int c = 0; c < top; ++c) {
+        int best = 0;
+        float value = -1.f;
+        for (int e = 0; e < experts; ++e)
+            if (z[e] > value) value = z[e], best = e;
+        ids[(size_t)t * top + c] = best;
+        weights[(size_t)t * top + c] = value * inv * scale;
+        z[best] = -2.f;                                    // (scores are positive: taken)
+    }
+    if (extra) shared_gate[t] = 1.0f / (1.0f + expf(-z[experts]));
+}
+
+__global__ void moe_plan_kernel(const int* __restrict__ ids, int pairs, int experts, int* __restrict__ offsets,
+                                int* __restrict__ order, int* __restrict__ inverse, int* __restrict__ tiles,
+                                int* __restrict__ n_tiles) {
+    __shared__ int counts[MOE_MAX_EXPERTS], starts[MOE_MAX_EXPERTS + 1], tile_starts[MOE_MAX_EXPERTS + 1];
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < experts) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tile = 0;
+        for (int e = 0; e < experts; ++e) {
+            starts[e] = at;
+            tile_starts[e] = tile;
+            at += counts[e];
+            tile += (counts[e] + TILE_M - 1) / TILE_M;
+        }
+        starts[experts] = at;
+        tile_starts[experts] = tile;
+        *n_tiles = tile;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = starts[e];
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        for (int k = tile_starts[e]; k < tile_starts[e + 1]; ++k) {
+            tiles[2 * k] = e;
+            tiles[2 * k + 1] = starts[e] + (k - tile_starts[e]) * TILE_M;
+        }
+        counts[e] = 0;                                     // (only this thread touched counts[e] since the barrier)
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e < 0 || e >= experts) continue;
+        const int r = starts[e] + atomicAdd(&counts[e], 1);
+        order[r] = p;
+        inverse[p] = r;
+    }
+}
+
+// MODE 0: out[r, n] = sum_k a[r, k] w_e[n, k] (32-bit out).  MODE 1: out[r, n] = u * silu(g), g = a . w_e[n], u = a . w_e[N + n].
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const T* __restrict__ a, long long lda, const int* __restrict__ order, int top,
+                const T* __restrict__ w, long long expert_stride, void* __restrict__ out_raw, long long ldo,
+                const int* __restrict__ offsets, const int* __restrict__ tiles, const int* __restrict__ n_tiles, int N, int K) {
+    __shared__ float as[TILE_K][TILE_M + 1];
+    __shared__ __align__(16) float ws[MODE == 1 ? 2 : 1][TILE_K][TILE_N];
+    __shared__ int source[TILE_M];
+    pdl_launch_dependents();
+    pdl_wait();
+    if ((int)blockIdx.x >= *n_tiles) return;
+    const int e = tiles[2 * blockIdx.x], row0 = tiles[2 * blockIdx.x + 1];
+    const int rows = min(TILE_M, offsets[e + 1] - row0);
+    const int n0 = blockIdx.y * TILE_N;
+    const T* we = w + (size_t)e * expert_stride;
+    if (threadIdx.x < TILE_M) {
+        int src = -1;
+        if ((int)threadIdx.x < rows) src = order ? order[row0 + threadIdx.x] / top : row0 + threadIdx.x;
+        source[threadIdx.x] = src;
+    }
+    __syncthreads();
+    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;      // rows 2 ty, 2 ty + 1; columns 4 tx .. 4 tx + 3
+    float acc[MODE == 1 ? 2 : 1][2][4] = {};
+    for (int k0 = 0; k0 < K; k0 += TILE_K) {
+        for (int idx = threadIdx.x; idx < TILE_M * TILE_K; idx += 256) {
+            const int r = idx / TILE_K, kk = idx % TILE_K;
+            const int src = source[r];
+            as[kk][r] = (src >= 0 && k0 + kk < K) ? to_float(a[(size_t)src * lda + k0 + kk]) : 0.f;
+        }
+        for (int idx = threadIdx.x; idx < TILE_N * TILE_K; idx += 256) {
+            const int n = idx / TILE_K, kk = idx % TILE_K;
+            const bool in = n0 + n < N && k0 + kk < K;
+            ws[0][kk][n] = in ? to_float(we[(size_t)(n0 + n) * K + k0 + kk]) : 0.f;
+            if (MODE == 1) ws[1][kk][n] = in ? to_float(we[(size_t)(N + n0 + n) * K + k0 + kk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < TILE_K; ++kk) {
+            const float a0 = as[kk][2 * ty], a1 = as[kk][2 * ty + 1];
+#pragma unroll
+            for (int m = 0; m < (MODE == 1 ? 2 : 1); ++m) {
+                const float4 b = *reinterpret_cast<const float4*>(&ws[m][kk][4 * tx]);
+                acc[m][0][0] = fmaf(a0, b.x, acc[m][0][0]);
+                acc[m][0][1] = fmaf(a0, b.y, acc[m][0][1]);
+                acc[m][0][2] = fmaf(a0, b.z, acc[m][0][2]);
+                acc[m][0][3] = fmaf(a0, b.w, acc[m][0][3]);
+                acc[m][1][0] = fmaf(a1, b.x, acc[m][1][0]);
+                acc[m][1][1] = fmaf(a1, b.y, acc[m][1][1]);
+                acc[m][1][2] = fmaf(a1, b.z, acc[m][1][2]);
+                acc[m][1][3] = fmaf(a1, b.w, acc[m][1][3]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int r = 2 * ty + x;
+        if (r >= rows) continue;
+#pragma unroll
+        for (int y = 0; y < 4; ++y) {
+            const int n = n0 + 4 * tx + y;
+            if (n >= N) continue;
+            if (MODE == 1) {
+                const float g = acc[0][x][y], u = acc[MODE == 1 ? 1 : 0][x][y];
+                reinterpret_cast<T*>(out_raw)[(size_t)(row0 + r) * ldo + n] = from_float<T>(u * (g / (1.0f + expf(-g))));
+            } else {
+                reinterpret_cast<float*>(out_raw)[(size_t)(row0 + r) * ldo + n] = acc[0][x][y];
+            }
+        }
+    }
+}
+
+__global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ y,
+                                   const int* __restrict__ inverse, const float* __restrict__ weights,
+                                   const float* __restrict__ shared_y, const float* __restrict__ shared_gate, int hidden,
+                                   int top, float alpha, int store) {
+    __shared__ int rows[MOE_MAX_TOP];
+    __shared__ float w[MOE_MAX_TOP];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    if ((int)threadIdx.x < top) {
+        rows[threadIdx.x] = inverse[(size_t)t * top + threadIdx.x];
+        w[threadIdx.x] = weights[(size_t)t * top + threadIdx.x];
+    }
+    __syncthreads();
+    const float gate = shared_y ? shared_gate[t] : 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float acc = 0.f;
+        for (int c = 0; c < top; ++c) acc = fmaf(w[c], y[(size_t)rows[c] * hidden + i], acc);
+        if (shared_y) acc = fmaf(gate, shared_y[(size_t)t * hidden + i], acc);
+        float* dst = residual + (size_t)t * hidden + i;
+        *dst = store ? alpha * acc : fmaf(alpha, acc, *dst);
+    }
+}
+}  // namespace
+
+LIA_EXPORT int lia_moe_tile_rows() { return TILE_M; }
+
+// x [n, ld] of `dtype`; router [experts + extra, hidden] 32-bit; ids, weights [n, top]; shared_gate [n] (extra = 1).
+LIA_EXPORT int lia_moe_route(const void* x, int dtype, long long ld, const float* router, int n, int hidden, int experts,
+                             int top, float scale, int extra, int* ids, float* weights, float* shared_gate,
+                             cudaStream_t stream) {
+    if (n <= 0) return LIA_OK;
+    if (hidden <= 0 || experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > experts || top > MOE_MAX_TOP ||
+        extra < 0 || extra > 1 || (extra && !shared_gate) || ld < hidden || (size_t)(hidden + experts + 1) * 4 > 200 * 1024)
+        return LIA_ERR_SIZE;
+    const size_t bytes = (size_t)(hidden + experts + extra) * sizeof(float);
+    static bool raised = false;
+    if (!raised) {
+        cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        raised = true;
+    }
+    if (dtype == LIA_F32)
+        return lia_launch(moe_route_kernel<float>, dim3(n), dim3(128), bytes, stream, (const float*)x, ld, router, hidden,
+                          experts, top, scale, extra, ids, weights, shared_gate);
+    if (dtype == LIA_BF16)
+        return lia_launch(moe_route_kernel<__nv_bfloat16>, dim3(n), dim3(128), bytes, stream, (const __nv_bfloat16*)x, ld,
+                          router, hidden, experts, top, scale, extra, ids, weights, shared_gate);
+    return LIA_ERR_DTYPE;
+}
+
+// ids [pairs]; offsets [experts + 1]; order, inverse [pairs]; tiles [2 * (pairs / TILE_M + experts)]; n_tiles [1].
+LIA_EXPORT int lia_moe_plan(const int* ids, int pairs, int experts, int* offsets, int* order, int* inverse, int* tiles,
+                            int* n_tiles, cudaStream_t stream) {
+    if (pairs <= 0) return LIA_OK;
+    if (experts <= 0 || experts > MOE_MAX_EXPERTS) return LIA_ERR_SIZE;
+    return lia_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, ids, pairs, experts, offsets, order, inverse, tiles,
+                      n_tiles);
+}
+
+// mode 1: a = the tokens' rows [n, lda] read through `order` (pair -> token pair / top), w [experts, 2 N, K], out
+// [pairs, ldo] of `dtype`.  mode 0: a = sorted rows [pairs, lda], w [experts, N, K], out [pairs, ldo] 32-bit.
+// `max_tiles`: pairs / TILE_M + min(experts, pairs), the most tiles the plan can list.
+LIA_EXPORT int lia_moe_gemm(int mode, const void* a, int dtype, long long lda, const int* order, int top, const void* w,
+                            void* out, long long ldo, const int* offsets, const int* tiles, const int* n_tiles,
+                            int max_tiles, int N, int K, cudaStream_t stream) {
+    if (max_tiles <= 0) return LIA_OK;
+    if (N <= 0 || K <= 0 || lda < K || ldo < N || top <= 0 || (mode != 0 && mode != 1) || (mode == 1 && !order))
+        return LIA_ERR_SIZE;
+    const dim3 grid(max_tiles, (N + TILE_N - 1) / TILE_N);
+    const long long stride = (long long)(mode == 1 ? 2 : 1) * N * K;
+#define LIA_MOE(T, MODE)                                                                                              \
+    return lia_launch(moe_gemm_kernel<T, MODE>, grid, dim3(256), 0, stream, (const T*)a, lda, order, top, (const T*)w, \
+                      stride, out, ldo, offsets, tiles, n_tiles, N, K)
+    if (dtype == LIA_F32) {
+        if (mode == 1) LIA_MOE(float, 1);
+        LIA_MOE(float, 0);
+    }
+    if (dtype == LIA_BF16) {
+        if (mode == 1) LIA_MOE(__nv_bfloat16, 1);
+        LIA_MOE(__nv_bfloat16, 0);
+    }
+#undef LIA_MOE
+    return LIA_ERR_DTYPE;
+}
+
+// residual [n, hidden] 32-bit (+)= alpha * (sum_c weights[t, c] y[inverse[t, c]] + shared_gate[t] shared_y[t]).
+LIA_EXPORT int lia_moe_combine(float* residual, const float* y, const int* inverse, const float* weights,
+                               const float* shared_y, const float* shared_gate, int n, int hidden, int top, float alpha,
+                               int store, cudaStream_t stream) {
+    if (n <= 0) return LIA_OK;
+    if (hidden <= 0 || top <= 0 || top > MOE_MAX_TOP || (shared_y && !shared_gate)) return LIA_ERR_SIZE;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    return lia_launch(moe_combine_kernel, dim3(n), dim3(threads), 0, stream, residual, y, inverse, weights, shared_y,
+                      shared_gate, hidden, top, alpha, store);
+}

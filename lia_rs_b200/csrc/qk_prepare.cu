@@ -35,7 +35,8 @@ __device__ __forceinline__ long long page_row(const int* __restrict__ block_tabl
 // One warp norms (optionally) and rotates one head that lies in `h` (shared memory, 32-bit, `d` elements; the rotated
 // span begins at `offset` and is `rot_dims` long), in place.
 __device__ __forceinline__ void norm_and_rotate(float* h, int d, const float* __restrict__ norm_weight, float eps,
-                                                int offset, int rot_dims, const float* rotation, int lane) {
+                                                int offset, int rot_dims, const float* rotation, int lane,
+                                                bool pairs = false) {
     if (norm_weight) {
         float sum = 0.f;
         for (int i = lane; i < d; i += 32) sum = fmaf(h[i], h[i], sum);
@@ -47,9 +48,10 @@ __device__ __forceinline__ void norm_and_rotate(float* h, int d, const float* __
     const int half = rot_dims / 2;
     for (int i = lane; i < half; i += 32) {
         const float c = rotation[i], s = rotation[half + i];
-        const float u = h[offset + i], v = h[offset + half + i];
-        h[offset + i] = u * c - v * s;
-        h[offset + half + i] = v * c + u * s;
+        const int a = offset + (pairs ? 2 * i : i), b = offset + (pairs ? 2 * i + 1 : half + i);
+        const float u = h[a], v = h[b];
+        h[a] = u * c - v * s;
+        h[b] = v * c + u * s;
     }
     __syncwarp();
 }
@@ -112,7 +114,7 @@ latent_prepare_kernel(const float* __restrict__ q_rows, long long ld_q, const fl
                       int rot_dims, const int* __restrict__ positions, const int* __restrict__ slots,
                       const int* __restrict__ block_table, int table_stride, T* __restrict__ q_plain,
                       T* __restrict__ q_rotated, T* __restrict__ latent_pages, T* __restrict__ key_pages, int n_tokens,
-                      int heads, int d, int dr, int rank, int page_size, int num_pages, int write_kv,
+                      int heads, int d, int dr, int rank, int page_size, int num_pages, int write_kv, int pairs,
                       int* __restrict__ error_flag) {
     extern __shared__ float prep_shared[];                 // [rot_dims] cosines then sines, then [PREP_WARPS][dr]
     __shared__ float scratch[32];
@@ -129,7 +131,8 @@ latent_prepare_kernel(const float* __restrict__ q_rows, long long ld_q, const fl
     float* parts = prep_shared + rot_dims;
     for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * freq[i], &rotation[half + i], &rotation[i]);
     __syncthreads();
-    const long long cache_row = write_kv ? page_row(block_table, table_stride, slot, pos, page_size, num_pages, error_flag) : -1;
+    const long long cache_row = (write_kv && shared_rows)
+                                    ? page_row(block_table, table_stride, slot, pos, page_size, num_pages, error_flag) : -1;
     // the queries: unrotated parts into the head's plane, rotated parts encoded
     const float* q = q_rows + (size_t)t * ld_q;
     float* part = parts + (size_t)warp * dr;
@@ -139,12 +142,14 @@ latent_prepare_kernel(const float* __restrict__ q_rows, long long ld_q, const fl
         for (int i = lane; i < d; i += 32) plain[i] = from_float<T>(src[i]);
         for (int i = lane; i < dr; i += 32) part[i] = src[d + i];
         __syncwarp();
-        norm_and_rotate(part, dr, nullptr, 0.f, 0, rot_dims, rotation, lane);
+        norm_and_rotate(part, dr, nullptr, 0.f, 0, rot_dims, rotation, lane, pairs != 0);
         T* rotated = q_rotated + ((size_t)t * heads + head) * dr;
         for (int i = lane; i < dr; i += 32) rotated[i] = from_float<T>(part[i]);
         __syncwarp();
     }
-    // the latent, normed over its own length, and the shared key part, encoded
+    // the latent, normed over its own length, and the shared key part, encoded (a layer that reads another layer's
+    // pages has neither)
+    if (!shared_rows) return;
     const float* s = shared_rows + (size_t)t * ld_s;
     float sum = 0.f;
     for (int i = threadIdx.x; i < rank; i += blockDim.x) sum = fmaf(s[i], s[i], sum);
@@ -158,7 +163,7 @@ latent_prepare_kernel(const float* __restrict__ q_rows, long long ld_q, const fl
     if (warp == 0) {
         for (int i = lane; i < dr; i += 32) parts[i] = s[rank + i];
         __syncwarp();
-        norm_and_rotate(parts, dr, nullptr, 0.f, 0, rot_dims, rotation, lane);
+        norm_and_rotate(parts, dr, nullptr, 0.f, 0, rot_dims, rotation, lane, pairs != 0);
         if (cache_row >= 0) {
             T* dst = key_pages + (size_t)cache_row * dr;
             for (int i = lane; i < dr; i += 32) dst[i] = from_float<T>(parts[i]);
@@ -195,23 +200,25 @@ LIA_EXPORT int lia_qkv_prepare(const float* rows, long long ld, const float* bia
 
 // q_rows [n, ld_q] 32-bit: per head d unrotated then dr rotated elements; shared_rows [n, ld_s] 32-bit: rank latent
 // elements then dr of the shared key part.  q_plain [heads, n, d], q_rotated [n, heads, dr], latent_pages [pages,
-// page_size, rank], key_pages [pages, page_size, dr], all of `dtype`.
+// page_size, rank], key_pages [pages, page_size, dr], all of `dtype`.  `pairs`: the rotation pairs element 2i with 2i+1
+// (0: i with i + rot_dims/2).  shared_rows null: only the queries are prepared (the pages are another layer's).
 LIA_EXPORT int lia_latent_prepare(const float* q_rows, long long ld_q, const float* shared_rows, long long ld_s,
                                   const float* latent_norm, float eps, const float* freq, int rot_dims,
                                   const int* positions, const int* slots, const int* block_table, int table_stride,
                                   void* q_plain, void* q_rotated, void* latent_pages, void* key_pages, int dtype,
                                   int n_tokens, int heads, int d, int dr, int rank, int page_size, int num_pages,
-                                  int write_kv, int* error_flag, cudaStream_t stream) {
+                                  int write_kv, int pairs, int* error_flag, cudaStream_t stream) {
     if (n_tokens <= 0) return LIA_OK;
     if (heads <= 0 || d <= 0 || dr <= 0 || rank <= 0 || page_size <= 0 || rot_dims < 0 || rot_dims > dr || (rot_dims & 1) ||
-        (rot_dims > 0 && !freq) || ld_q < (long long)heads * (d + dr) || ld_s < rank + dr || !latent_norm || dr > 4096)
+        (rot_dims > 0 && !freq) || ld_q < (long long)heads * (d + dr) || (shared_rows && (ld_s < rank + dr || !latent_norm)) ||
+        dr > 4096)
         return LIA_ERR_SIZE;
     const size_t smem = ((size_t)rot_dims + (size_t)PREP_WARPS * dr) * sizeof(float);
 #define LIA_PREP(T)                                                                                                  \
     return lia_launch(latent_prepare_kernel<T>, dim3(n_tokens), dim3(PREP_WARPS * 32), smem, stream, q_rows, ld_q,   \
                       shared_rows, ld_s, latent_norm, eps, freq, rot_dims, positions, slots, block_table,            \
                       table_stride, (T*)q_plain, (T*)q_rotated, (T*)latent_pages, (T*)key_pages, n_tokens, heads, d, \
-                      dr, rank, page_size, num_pages, write_kv, error_flag)
+                      dr, rank, page_size, num_pages, write_kv, pairs, error_flag)
     if (dtype == LIA_BF16) LIA_PREP(__nv_bfloat16);
     if (dtype == LIA_F32) LIA_PREP(float);
 #undef LIA_PREP

@@ -105,7 +105,7 @@ class _Signatures:
                        c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     lia_latent_prepare = [c_void_p, ctypes.c_longlong, c_void_p, ctypes.c_longlong, c_void_p, c_float, c_void_p, c_int,
                           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                          c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     lia_causal_conv = [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     lia_conv_state_update = [c_void_p, ctypes.c_longlong, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_int, c_int,
@@ -121,6 +121,24 @@ class _Signatures:
     lia_latent_attention = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
     lia_gemm_mma_batched_accepts = [c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_int, c_int, c_int]
+    lia_embedding_streams = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
+    lia_hyper_step = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                      c_int, c_int, c_float, c_void_p]
+    lia_softcap_rows = [c_void_p, ctypes.c_longlong, c_int, c_int, c_float, c_void_p]
+    lia_gate_rows = [c_void_p, c_int, ctypes.c_longlong, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_void_p]
+    lia_moe_tile_rows = []
+    lia_moe_route = [c_void_p, c_int, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+                     c_void_p, c_void_p, c_void_p]
+    lia_moe_plan = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+    lia_moe_gemm = [c_int, c_void_p, c_int, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong,
+                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lia_moe_combine = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int,
+                       c_void_p]
+    lia_retention_chunks = [c_int, c_int]
+    lia_retention_encode = [c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                            c_void_p]
+    lia_retention = [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_void_p,
+                     c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, ctypes.c_longlong, c_void_p]
     lia_gemm_mma_batched = [c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_int, c_int, c_int, c_int, c_void_p]
 
 def dtype_code(dtype: torch.dtype) -> int:
@@ -887,25 +905,30 @@ def qkv_prepare(rows, bias, q_norm, k_norm, eps, freq, rot_dims, vmix_mode, vmix
 
 
 def latent_prepare(q_rows, shared_rows, latent_norm, eps, freq, rot_dims, positions, slots, block_table, q_plain,
-                   q_rotated, latent_pages, key_pages, heads, d, dr, rank, write_kv=True, error_flag=None):
+                   q_rotated, latent_pages, key_pages, heads, d, dr, rank, write_kv=True, error_flag=None, pairs=False):
     """For attention through a latent: norm and append of the latent, encoding and append of the shared key part,
     the queries' unrotated parts as planes [heads, tokens, d] and their rotated parts encoded [tokens, heads dr]; see
-    csrc/qk_prepare.cu."""
+    csrc/qk_prepare.cu.  `pairs`: the rotation pairs element 2i with 2i + 1 (else i with i + rot_dims / 2).
+    `shared_rows` None: only the queries are prepared (the pages are filled by another layer)."""
     _cuda(latent_norm, freq, positions, slots, block_table, q_plain, q_rotated, latent_pages, key_pages, error_flag)
     _f32(q_rows, shared_rows, latent_norm, freq)
     n = q_rows.shape[0]
-    if q_rows.stride(1) != 1 or shared_rows.stride(1) != 1 or q_rows.shape[1] < heads * (d + dr) or \
-            shared_rows.shape[1] < rank + dr or shared_rows.shape[0] != n:
-        raise KernelError("latent_prepare takes 32-bit query rows and shared rows of one step")
+    if q_rows.stride(1) != 1 or q_rows.shape[1] < heads * (d + dr):
+        raise KernelError("latent_prepare takes 32-bit query rows of one step")
+    if shared_rows is not None and (shared_rows.stride(1) != 1 or shared_rows.shape[1] < rank + dr or
+                                    shared_rows.shape[0] != n or latent_norm is None):
+        raise KernelError("latent_prepare takes 32-bit shared rows of the step and the latent's norm weight")
     if not (q_plain.dtype == q_rotated.dtype == latent_pages.dtype == key_pages.dtype) or q_plain.numel() != heads * n * d \
             or q_rotated.numel() != n * heads * dr or latent_pages.shape[-1] != rank or key_pages.shape[-1] != dr:
         raise KernelError("latent_prepare: outputs and pages must have one element type and the parts' sizes")
     with _timed("latent_prepare"):
-        _check(lib().lia_latent_prepare(_p(q_rows), q_rows.stride(0), _p(shared_rows), shared_rows.stride(0),
+        _check(lib().lia_latent_prepare(_p(q_rows), q_rows.stride(0), _p(shared_rows),
+                                        0 if shared_rows is None else shared_rows.stride(0),
                                         _p(latent_norm), float(eps), _p(freq), int(rot_dims), _p(positions), _p(slots),
                                         _p(block_table), block_table.shape[1], _p(q_plain), _p(q_rotated),
                                         _p(latent_pages), _p(key_pages), dtype_code(q_plain.dtype), n, heads, d, dr, rank,
-                                        latent_pages.shape[1], latent_pages.shape[0], 1 if write_kv else 0,
+                                        latent_pages.shape[1], latent_pages.shape[0],
+                                        1 if write_kv and shared_rows is not None else 0, 1 if pairs else 0,
                                         _p(error_flag), _stream()), "latent_prepare")
 
 
@@ -1051,3 +1074,168 @@ def gemm_mma_batched(a, w, out, label=None):
         raise KernelError("gemm_mma_batched is a bfloat16 kernel")
     with _timed("gemm_mma_batched", label, work=lambda: _batched_work(a, w, out)):
         _check(lib().lia_gemm_mma_batched(*pointers, B, M, N, K, _stream()), "gemm_mma_batched")
+
+
+# ---- several residual streams (hyper-connections), row-wise gates and the logits' soft cap: csrc/hyper_connections.cu ----
+HYPER_MAX_STREAMS = 8
+GATE_SIGMOID, GATE_SILU = 1, 2
+
+
+def embedding_streams(tokens, table, out, streams: int, scale: float = 1.0, error_flag=None):
+    """out [n, streams * hidden] 32-bit: every stream of a token starts as its row of the table times `scale`."""
+    _cuda(tokens, table, out, error_flag)
+    _f32(out)
+    n, hidden = out.shape[0], table.shape[1]
+    if out.shape[1] != streams * hidden:
+        raise KernelError("embedding_streams: the rows hold `streams` copies of the table's width")
+    with _timed("embedding_streams"):
+        _check(lib().lia_embedding_streams(_p(tokens), _p(table), dtype_code(table.dtype), _p(out), n, hidden, int(streams),
+                                           table.shape[0], float(scale), _p(error_flag), _stream()), "embedding_streams")
+
+
+def hyper_step(x, streams: int, y=None, mix=None, out_weights=None, in_weights=None, rows_index=None, u=None,
+               norm_weight=None, normed=None, eps: float = 0.0):
+    """One pass over the rows of x [n, streams * hidden] (32-bit, the streams of a token side by side).  With y [n, hidden]:
+    x_t <- sum_s mix[s, t] x_s + out_weights[t] y, in place.  With u [rows, hidden]: u = sum_s in_weights[s] x_s (the
+    plain sum without `in_weights`) of the new streams, and with `normed` also normed = u / sqrt(mean(u^2) + eps) *
+    norm_weight in normed's element type.  `rows_index` (without y): row r is read from row rows_index[r]."""
+    _cuda(x, y, mix, out_weights, in_weights, rows_index, u, norm_weight, normed)
+    _f32(x, y, mix, out_weights, in_weights, u, norm_weight)
+    hidden = x.shape[1] // streams
+    rows = (y if y is not None else u).shape[0]
+    if x.shape[1] != streams * hidden or (y is not None and tuple(y.shape) != (rows, hidden)) or \
+            (u is not None and tuple(u.shape) != (rows, hidden)) or (normed is not None and tuple(normed.shape) != (rows, hidden)) \
+            or (mix is not None and mix.numel() != streams * streams) or (rows_index is None and x.shape[0] < rows):
+        raise KernelError("hyper_step: shapes do not agree")
+    with _timed("hyper_step", nbytes=rows * hidden * 4 * (streams * (2 if y is not None else 1) + 2)):
+        _check(lib().lia_hyper_step(_p(x), _p(y), _p(mix), _p(out_weights), _p(in_weights), _p(rows_index), _p(u),
+                                    _p(norm_weight), _p(normed), 0 if normed is None else dtype_code(normed.dtype), rows,
+                                    hidden, int(streams), float(eps), _stream()), "hyper_step")
+
+
+def softcap_rows(z, cap: float):
+    """z <- cap * tanh(z / cap) on 32-bit rows, in place."""
+    _f32(z)
+    if not z.is_cuda or z.dim() != 2 or z.stride(1) != 1:
+        raise KernelError("softcap_rows takes 32-bit CUDA rows")
+    with _timed("softcap_rows"):
+        _check(lib().lia_softcap_rows(_p(z), z.stride(0), z.shape[0], z.shape[1], float(cap), _stream()), "softcap_rows")
+
+
+def gate_rows(o, g, act: int):
+    """o <- o * f(g) element by element, f the logistic function (`GATE_SIGMOID`) or SiLU (`GATE_SILU`); g 32-bit rows (a
+    slice of wider rows will do), o rows of the compute element type."""
+    _f32(g)
+    if not (o.is_cuda and g.is_cuda) or o.dim() != 2 or g.dim() != 2 or o.stride(1) != 1 or g.stride(1) != 1 or \
+            tuple(o.shape) != tuple(g.shape):
+        raise KernelError("gate_rows: rows of one shape")
+    with _timed("gate_rows"):
+        _check(lib().lia_gate_rows(_p(o), dtype_code(o.dtype), o.stride(0), _p(g), g.stride(0), o.shape[0], o.shape[1],
+                                   int(act), _stream()), "gate_rows")
+
+
+# ---- a mixture of gated experts: csrc/moe.cu ----
+MOE_MAX_EXPERTS, MOE_MAX_TOP = 1024, 32
+
+
+def moe_tile_rows() -> int:
+    return int(lib().lia_moe_tile_rows())
+
+
+def moe_max_tiles(pairs: int, experts: int) -> int:
+    """The most row tiles that `pairs` (token, choice) pairs grouped by expert can be cut into."""
+    return pairs // moe_tile_rows() + min(experts, pairs)
+
+
+def moe_route(x, router, top: int, scale: float, ids, weights, shared_gate=None):
+    """Router scores in 32-bit, the `top` largest chosen: ids, weights [n, top]; with one more row in `router` than
+    experts, shared_gate [n] = the logistic function of that row's product."""
+    _cuda(x, router, ids, weights, shared_gate)
+    _f32(router, weights, shared_gate)
+    n, hidden = x.shape
+    extra = 0 if shared_gate is None else 1
+    experts = router.shape[0] - extra
+    if router.shape[1] != hidden or tuple(ids.shape) != (n, top) or tuple(weights.shape) != (n, top) or ids.dtype != torch.int32:
+        raise KernelError("moe_route: shapes do not agree")
+    with _timed("moe_route"):
+        _check(lib().lia_moe_route(_p(x), dtype_code(x.dtype), x.stride(0), _p(router), n, hidden, experts, int(top),
+                                   float(scale), extra, _p(ids), _p(weights), _p(shared_gate), _stream()), "moe_route")
+
+
+def moe_plan(ids, experts: int, offsets, order, inverse, tiles, n_tiles):
+    """The pairs grouped by expert: offsets [experts + 1], order and inverse [pairs], the tile list and its length."""
+    _cuda(ids, offsets, order, inverse, tiles, n_tiles)
+    pairs = ids.numel()
+    if offsets.numel() < experts + 1 or order.numel() < pairs or inverse.numel() < pairs or \
+            tiles.numel() < 2 * moe_max_tiles(pairs, experts):
+        raise KernelError("moe_plan: a list is too short")
+    with _timed("moe_plan"):
+        _check(lib().lia_moe_plan(_p(ids), pairs, int(experts), _p(offsets), _p(order), _p(inverse), _p(tiles), _p(n_tiles),
+                                  _stream()), "moe_plan")
+
+
+def moe_gemm(gated: bool, a, order, top: int, w, out, offsets, tiles, n_tiles, max_tiles: int, label=None):
+    """The experts' products over the planned tiles.  `gated`: a = the tokens' rows, read through `order`; w [experts,
+    2 N, K] = [gate; up]; out [pairs, N] = up * silu(gate) in the compute element type.  Else a = sorted rows [pairs, K],
+    w [experts, N, K], out [pairs, N] 32-bit."""
+    _cuda(a, order, w, out, offsets, tiles, n_tiles)
+    N, K = out.shape[1], a.shape[1]
+    if w.dim() != 3 or w.shape[1] != (2 * N if gated else N) or w.shape[2] != K or a.dtype != w.dtype or \
+            out.dtype != (a.dtype if gated else torch.float32):
+        raise KernelError("moe_gemm: shapes or element types do not agree")
+    pairs = out.shape[0]
+    with _timed("moe_gemm", label, nbytes=w.numel() * w.element_size(), flops=2 * pairs * w.shape[1] * K):
+        _check(lib().lia_moe_gemm(1 if gated else 0, _p(a), dtype_code(a.dtype), a.stride(0), _p(order), int(top), _p(w),
+                                  _p(out), out.stride(0), _p(offsets), _p(tiles), _p(n_tiles), int(max_tiles), N, K,
+                                  _stream()), "moe_gemm")
+
+
+def moe_combine(residual, y, inverse, weights, shared_y, shared_gate, top: int, alpha: float, store: bool):
+    """residual (+)= alpha * (sum_c weights[t, c] y[inverse[t, c]] + shared_gate[t] shared_y[t])."""
+    _cuda(residual, y, inverse, weights, shared_y, shared_gate)
+    _f32(residual, y, weights, shared_y, shared_gate)
+    n, hidden = residual.shape
+    with _timed("moe_combine"):
+        _check(lib().lia_moe_combine(_p(residual), _p(y), _p(inverse), _p(weights), _p(shared_y), _p(shared_gate), n, hidden,
+                                     int(top), float(alpha), 1 if store else 0, _stream()), "moe_combine")
+
+
+# ---- retention (a decayed linear recurrence per head): csrc/retention.cu ----
+RETENTION_MAX_HEAD = 256
+
+
+def retention_chunks(portion_tokens: int, n_segments: int) -> int:
+    return int(lib().lia_retention_chunks(int(portion_tokens), int(n_segments)))
+
+
+def retention_scratch_floats(chunks: int, heads: int, d: int, dv: int) -> int:
+    return chunks * heads * d * dv
+
+
+def retention_encode(rows, freq, rot_dims: int, positions, slots, heads: int, d: int, k_scale: float):
+    """rows [n, >= 2 heads d] 32-bit, q then k: both rotated in halves over the first rot_dims elements of each head, k
+    then multiplied by k_scale, in place."""
+    _cuda(freq, positions, slots)
+    _f32(rows, freq)
+    if rows.stride(1) != 1:
+        raise KernelError("retention_encode takes 32-bit rows")
+    with _timed("retention_encode"):
+        _check(lib().lia_retention_encode(_p(rows), rows.stride(0), _p(freq), int(rot_dims), _p(positions), _p(slots),
+                                          rows.shape[0], heads, d, float(k_scale), _stream()), "retention_encode")
+
+
+def retention(rows, decay, state, segments, n_segments: int, max_chunks: int, single_rows, slots, out, heads: int, d: int,
+              dv: int, eps: float, scratch=None):
+    """S <- decay_h S + k v^T, o = S^T q, out = o / rms(o) * silu(g) along the step's runs; rows [n, 2 heads (d + dv)]
+    32-bit = [q | k | v | g] as `retention_encode` left them, state [slots, heads, d, dv] 32-bit."""
+    _cuda(decay, segments, single_rows, slots, out, scratch)
+    _f32(rows, decay, state, scratch)
+    n_single = 0 if single_rows is None else single_rows.numel()
+    if rows.stride(1) != 1 or rows.shape[1] < 2 * heads * (d + dv) or tuple(out.shape) != (rows.shape[0], heads * dv) or \
+            state[0].numel() != heads * d * dv or not state[0].is_contiguous():
+        raise KernelError("retention: shapes do not agree")
+    with _timed("retention", nbytes=rows.numel() * 4, flops=4 * rows.shape[0] * heads * d * dv):
+        _check(lib().lia_retention(_p(rows), rows.stride(0), _p(decay), _p(state), state.stride(0), _p(segments),
+                                   int(n_segments), int(max_chunks), _p(single_rows), n_single, _p(slots), _p(out),
+                                   dtype_code(out.dtype), heads, d, dv, float(eps), _p(scratch),
+                                   0 if scratch is None else scratch.numel(), _stream()), "retention")

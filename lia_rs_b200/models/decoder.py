@@ -43,6 +43,8 @@ class ModelSpec:
     eos_token_ids: tuple = ()
     position_table_name: Optional[str] = None       # a learned vector per position [max_positions, hidden], added to the embedding
     junctions: dict = field(default_factory=dict)   # schedule position -> PartSpec of a junction that runs ahead of that entry
+    streams: int = 1                                # copies of the residual stream in a token's row (hyper-connections); all start as the embedding output, their sum goes to the final norm
+    logit_softcap: Optional[float] = None           # logits <- cap * tanh(logits / cap)
 
     def __post_init__(self):
         if not self.schedule:
@@ -54,6 +56,12 @@ class ModelSpec:
                 raise ValueError(f"schedule names layer {entry.layer}, the model has {len(self.layers)}")
         for layer in self.layers:
             check_layer(layer)                      # a size that a part or its kernels cannot take is refused here
+            if lookup(ARRANGEMENTS, layer.arrangement, "arrangement").streams(layer) != self.streams:
+                raise ValueError(f"the model keeps {self.streams} residual streams; a layer's arrangement keeps another number")
+        if self.streams != 1 and self.junctions:
+            raise ValueError("junctions act on a single residual stream")
+        if self.logit_softcap is not None and not float(self.logit_softcap) > 0:
+            raise ValueError("logit_softcap must be positive")
         for position, junction in self.junctions.items():
             if not 0 <= position < len(self.schedule):
                 raise ValueError(f"a junction is attached to schedule position {position}, the schedule has {len(self.schedule)}")
@@ -147,6 +155,8 @@ class DecoderModel:
         norm_cls = lookup(NORMS, spec.final_norm.kind, "norm")
         names = [s.name for s in norm_cls.tensor_specs(spec.final_norm.params, spec.final_norm_prefix)]
         self.final_norm = norm_cls(spec.final_norm.params, on_device(names), spec.final_norm_prefix, runtime)
+        record = self.final_norm.rms_record()
+        self._final_weight = record[0].to(torch.float32).contiguous() if record is not None else None
         if spec.head_name is None:
             self.head = self.embedding
         else:
@@ -181,9 +191,14 @@ class DecoderModel:
         the last layer, src/inference/llama_fusion.rs:45-60, src/gpu/kernels/llama.rs:185-198)."""
         rt, spec = self.runtime, self.spec
         n = ctx.n_tokens
-        h = ctx.buffer("model.h", (n, spec.hidden_size), torch.float32)
+        streams = spec.streams
+        h = ctx.buffer("model.h", (n, streams * spec.hidden_size), torch.float32)
         first = ctx.buffer("model.h0", (n, spec.hidden_size), torch.float32) if self._keeps_first else None
-        if self.position_table is not None:
+        if streams > 1:
+            if self.position_table is not None:
+                raise ValueError("a position table with several residual streams is not built")
+            rt.ops.embedding_streams(ctx.tokens, self.embedding, h, streams, spec.embedding_scale, ctx.error_flag)
+        elif self.position_table is not None:
             rt.ops.embedding_positions(ctx.tokens, ctx.positions, self.embedding, self.position_table, h,
                                        spec.embedding_scale, copy=first, error_flag=ctx.error_flag)
         else:
@@ -206,10 +221,22 @@ class DecoderModel:
         if ctx.n_out == 0:
             return ctx.logits_buffer(0, spec.vocab_size)
         y = ctx.buffer("model.y", (ctx.n_out, spec.hidden_size), rt.compute_dtype)
-        if picked is not None:
+        if streams > 1:
+            # the wanted rows' streams are added up, and normed in the same pass where the final norm is an RMS norm
+            total = ctx.buffer("model.sum", (ctx.n_out, spec.hidden_size), torch.float32)
+            record = self.final_norm.rms_record()
+            if record is not None:
+                rt.ops.hyper_step(h, streams, rows_index=ctx.out_rows, u=total, norm_weight=self._final_weight, normed=y,
+                                  eps=record[1])
+            else:
+                rt.ops.hyper_step(h, streams, rows_index=ctx.out_rows, u=total)
+                self.final_norm.forward(ctx, total, y)
+        elif picked is not None:
             self.final_norm.forward(ctx, picked, y)
         else:
             self.final_norm.forward(ctx, h, y, rows_index=ctx.out_rows)
         logits = ctx.logits_buffer(ctx.n_out, spec.vocab_size)
         linear(rt, STORE, y, self.head, logits, spec.logit_scale, error_flag=ctx.error_flag, name="head")
+        if spec.logit_softcap is not None:
+            rt.ops.softcap_rows(logits, float(spec.logit_softcap))
         return logits

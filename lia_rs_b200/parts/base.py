@@ -211,6 +211,12 @@ class Arrangement:
         for one is handed the tensor [slots, *shape] as `own_state` at every `forward`."""
         return None
 
+    @staticmethod
+    def streams(layer_spec) -> int:
+        """How many copies of the residual stream the layer keeps side by side in a token's row (the model gives every
+        layer rows of `streams * hidden` elements; all layers of a model agree)."""
+        return 1
+
     def graph_key(self, ctx) -> tuple:
         """As `Part.graph_key`, for the layer: what its parts answer, put together.  The default is the answer that
         is always right."""

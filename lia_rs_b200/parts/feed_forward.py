@@ -20,6 +20,7 @@ class SwiGLU(FeedForward):
     def graph_key(self, ctx) -> tuple:
         return ()                    # rows in, rows out: only the number of tokens matters
     takes_deferred_norm = True
+    can_store = True
 
     NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
 
@@ -41,11 +42,11 @@ class SwiGLU(FeedForward):
         self.w_gate_up = prepare_weight(torch.cat([tensors[gate], tensors[up]], dim=0), runtime)
         self.w_down = prepare_weight(tensors[down], runtime)
 
-    def forward(self, ctx, x, residual, scale):
+    def forward(self, ctx, x, residual, scale, store=False):
         rt, n = self.runtime, x.shape[0]
         act = ctx.buffer("ffn.act", (n, self.intermediate), rt.compute_dtype)
         linear(rt, SWIGLU, x, self.w_gate_up, act, error_flag=ctx.error_flag, name="gate_up")
-        linear(rt, ACCUM, act, self.w_down, residual, scale, error_flag=ctx.error_flag, name="down")
+        linear(rt, STORE if store else ACCUM, act, self.w_down, residual, scale, error_flag=ctx.error_flag, name="down")
 
 
 @register_feed_forward("dense_act")

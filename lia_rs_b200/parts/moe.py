@@ -1,0 +1,110 @@
+"""A mixture of gated feed-forward experts.
+
+    z = W_router x  (32-bit),  s = softmax(z) over all experts
+    the `top` experts with the largest s are chosen (the lower index wins a tie); weight_e = s_e * router_scale,
+        not renormalised over the chosen
+    expert_e(x) = W_down,e (silu(W_gate,e x) * (W_up,e x))
+    f(x) = sum over the chosen e of weight_e expert_e(x)  [+ sigmoid(w_sg . x) * shared(x)]
+
+`shared` (optional) is one more expert of a size of its own that every token uses, times a gate of one number per token.
+The router's product, the softmax, the choice and the weights are 32-bit; the (token, choice) pairs are grouped by expert
+on the device, each expert's rows go through its two products in tiles, and one kernel adds a token's weighted rows, in
+the order of its choices, into the residual stream (csrc/moe.cu).  Nothing is decided on the host, so a step's launches
+depend on its number of tokens alone, and a token's result does not depend on what else is in the batch.
+
+Parameters: hidden, experts, top, intermediate, router_scale, shared ({"intermediate": n} or None), and optionally
+`names`.  Checkpoint names behind the part's prefix: router, e<i>.gate, e<i>.up, e<i>.down, shared.gate, shared.up,
+shared.down, shared.sg."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights import TensorSpec
+from .base import FeedForward, register_feed_forward
+from .linear import STORE, SWIGLU, linear, prepare_weight
+
+
+@register_feed_forward("expert_mixture")
+class ExpertMixture(FeedForward):
+    graph_safe = True
+    can_store = True
+    NAMES = {"router": "router", "expert": "e{}.", "gate": "gate", "up": "up", "down": "down", "shared": "shared.",
+             "shared_gate": "shared.sg"}
+
+    def graph_key(self, ctx) -> tuple:
+        return ()
+
+    @staticmethod
+    def _names(params, prefix):
+        return {key: name for key, name in {**ExpertMixture.NAMES, **params.get("names", {})}.items()}
+
+    @staticmethod
+    def check_params(params):
+        experts, top = int(params["experts"]), int(params["top"])
+        if not 0 < experts <= ops.MOE_MAX_EXPERTS or not 0 < top <= min(experts, ops.MOE_MAX_TOP):
+            raise ValueError(f"expert mixture: 1..{ops.MOE_MAX_EXPERTS} experts, of which 1..{ops.MOE_MAX_TOP} (at most all) "
+                             "are chosen")
+        if int(params["intermediate"]) <= 0 or (params.get("shared") and int(params["shared"]["intermediate"]) <= 0):
+            raise ValueError("expert mixture: the experts' sizes must be positive")
+
+    @staticmethod
+    def tensor_specs(params, prefix):
+        h, experts, ff = int(params["hidden"]), int(params["experts"]), int(params["intermediate"])
+        n = ExpertMixture._names(params, prefix)
+        specs = []
+        for e in range(experts):
+            p = prefix + n["expert"].format(e)
+            specs += [TensorSpec(p + n["gate"], (ff, h)), TensorSpec(p + n["up"], (ff, h)), TensorSpec(p + n["down"], (h, ff))]
+        specs.append(TensorSpec(prefix + n["router"], (experts, h)))
+        if params.get("shared"):
+            ffs, p = int(params["shared"]["intermediate"]), prefix + n["shared"]
+            specs += [TensorSpec(p + n["gate"], (ffs, h)), TensorSpec(p + n["up"], (ffs, h)), TensorSpec(p + n["down"], (h, ffs)),
+                      TensorSpec(prefix + n["shared_gate"], (1, h))]
+        return specs
+
+    def __init__(self, params, tensors, prefix, runtime):
+        super().__init__(params, tensors, prefix, runtime)
+        self.check_params(params)
+        self.hidden, self.experts, self.top = int(params["hidden"]), int(params["experts"]), int(params["top"])
+        self.ff, self.router_scale = int(params["intermediate"]), float(params["router_scale"])
+        n = self._names(params, prefix)
+        expert = lambda e, key: tensors[prefix + n["expert"].format(e) + n[key]]
+        self.w_gate_up = prepare_weight(torch.stack([torch.cat([expert(e, "gate"), expert(e, "up")], dim=0)
+                                                     for e in range(self.experts)]), runtime)       # [E, 2 ff, hidden]
+        self.w_down = prepare_weight(torch.stack([expert(e, "down") for e in range(self.experts)]), runtime)   # [E, hidden, ff]
+        router = [tensors[prefix + n["router"]]]
+        self.shared = bool(params.get("shared"))
+        if self.shared:
+            self.ffs, p = int(params["shared"]["intermediate"]), prefix + n["shared"]
+            router.append(tensors[prefix + n["shared_gate"]].view(1, self.hidden))        # the gate's row rides on the router's product
+            self.w_shared_gate_up = prepare_weight(torch.cat([tensors[p + n["gate"]], tensors[p + n["up"]]], dim=0), runtime)
+            self.w_shared_down = prepare_weight(tensors[p + n["down"]], runtime)
+        self.router = torch.cat(router, dim=0).to(torch.float32).contiguous()
+
+    def forward(self, ctx, x, residual, scale, store=False):
+        rt, n = self.runtime, x.shape[0]
+        top, experts, dtype = self.top, self.experts, rt.compute_dtype
+        pairs = n * top
+        scratch = ctx.runtime.scratch
+        ids = scratch("moe.ids", pairs, torch.int32).view(n, top)
+        weights = scratch("moe.weights", pairs, torch.float32).view(n, top)
+        shared_gate = scratch("moe.shared_gate", n, torch.float32) if self.shared else None
+        ops.moe_route(x, self.router, top, self.router_scale, ids, weights, shared_gate)
+        max_tiles = ops.moe_max_tiles(pairs, experts)
+        lists = scratch("moe.lists", experts + 2 + 2 * pairs + 2 * max_tiles, torch.int32)
+        offsets, n_tiles = lists[:experts + 1], lists[experts + 1:experts + 2]
+        order, inverse = lists[experts + 2:experts + 2 + pairs], lists[experts + 2 + pairs:experts + 2 + 2 * pairs]
+        tiles = lists[experts + 2 + 2 * pairs:]
+        ops.moe_plan(ids.view(-1), experts, offsets, order, inverse, tiles, n_tiles)
+        act = scratch("moe.act", pairs * self.ff, dtype).view(pairs, self.ff)
+        ops.moe_gemm(True, x, order, top, self.w_gate_up, act, offsets, tiles, n_tiles, max_tiles, label="gate_up")
+        y = scratch("moe.y", pairs * self.hidden, torch.float32).view(pairs, self.hidden)
+        ops.moe_gemm(False, act, None, top, self.w_down, y, offsets, tiles, n_tiles, max_tiles, label="down")
+        shared_y = None
+        if self.shared:
+            shared_act = ctx.buffer("moe.shared_act", (n, self.ffs), dtype)
+            linear(rt, SWIGLU, x, self.w_shared_gate_up, shared_act, error_flag=ctx.error_flag, name="shared_gate_up")
+            shared_y = ctx.buffer("moe.shared_y", (n, self.hidden), torch.float32)
+            linear(rt, STORE, shared_act, self.w_shared_down, shared_y, error_flag=ctx.error_flag, name="shared_down")
+        ops.moe_combine(residual, y, inverse, weights, shared_y, shared_gate, top, scale, store)

@@ -20,7 +20,11 @@ c, and `rot_dim` more that are one rotated key part for all heads.  Head h's key
 W_uv,h c.  The pages hold c and the rotated part only (the cache's "keys" are the latents, its "values" the rotated
 parts), so attention runs in the latent's space: the unrotated query is taken through W_uk,h^T once per token,
 q~_h = W_uk,h^T q_h, the score is scale (q~_h . c_j + q_rot,h . r_j), the weighted sum of the latents is taken through
-W_uv,h afterwards, and the heads side by side through W_o.  A window as above; no sink.
+W_uv,h afterwards, and the heads side by side through W_o.  A window as above; no sink.  Options: `q_rank` None: the
+queries come straight from the input, q = W_q x; `rot_pairs`: the rotation pairs element 2i with 2i + 1 instead of i with
+i + dims / 2; `gate` "sigmoid": the heads side by side are multiplied by sigmoid(W_g x) ahead of W_o; `shared_cache`: the
+layer has no W_dkv and reads the latents and rotated parts that another layer of the same sizes and rotation put into the
+pages (the model's schedule names that layer's cache), with W_uk, W_uv and queries of its own.
 
 Scores, softmax, norms and angles are 32-bit in both.  Which kernel serves which rows: the kernel for every size and
 element type (csrc/attention_generic.cu, `attention_general`); `sink_attention` in bfloat16 with equal key and value
@@ -166,8 +170,8 @@ class LatentAttention(Mixer):
     graph_safe = True
     takes_deferred_norm = True
     can_store = True
-    NAMES = {"q_down": "dq", "q_norm": "dq.norm", "q_up": "uq", "kv_down": "dkv", "kv_norm": "dkv.norm", "k_up": "uk",
-             "v_up": "uv", "o": "o"}
+    NAMES = {"q_down": "dq", "q_norm": "dq.norm", "q_up": "uq", "q": "q", "kv_down": "dkv", "kv_norm": "dkv.norm",
+             "k_up": "uk", "v_up": "uv", "gate": "g", "o": "o"}
 
     def graph_key(self, ctx) -> tuple:
         return ()
@@ -178,24 +182,35 @@ class LatentAttention(Mixer):
 
     @staticmethod
     def check_params(params):
-        for key in ("heads", "head_dim", "rot_dim", "v_head_dim", "kv_rank", "q_rank"):
+        for key in ("heads", "head_dim", "rot_dim", "v_head_dim", "kv_rank"):
             if int(params[key]) <= 0:
                 raise ValueError(f"latent attention: {key} must be positive")
+        if params.get("q_rank") is not None and int(params["q_rank"]) <= 0:
+            raise ValueError("latent attention: q_rank must be positive, or None for queries straight from the input")
         if int(params["kv_rank"]) + int(params["rot_dim"]) > 1024 or int(params["kv_rank"]) > 512:
             raise ValueError("latent attention: kv_rank at most 512 and kv_rank + rot_dim at most 1024 (what the kernel takes)")
         _check_rot(params.get("rot"), int(params["rot_dim"]), "latent attention")
         if params.get("window") is not None and int(params["window"]) <= 0:
             raise ValueError("latent attention: window must be positive or None")
+        if params.get("gate") not in (None, "sigmoid"):
+            raise ValueError("latent attention: gate is None or 'sigmoid'")
 
     @staticmethod
     def tensor_specs(params, prefix):
-        h, H, d, dr, dv, rank, q_rank = (int(params[k]) for k in ("hidden", "heads", "head_dim", "rot_dim", "v_head_dim",
-                                                                   "kv_rank", "q_rank"))
+        h, H, d, dr, dv, rank = (int(params[k]) for k in ("hidden", "heads", "head_dim", "rot_dim", "v_head_dim", "kv_rank"))
         n = LatentAttention._names(params, prefix)
-        return [TensorSpec(n["q_down"], (q_rank, h)), TensorSpec(n["q_norm"], (q_rank,), kind="norm"),
-                TensorSpec(n["q_up"], (H * (d + dr), q_rank)), TensorSpec(n["kv_down"], (rank + dr, h)),
-                TensorSpec(n["kv_norm"], (rank,), kind="norm"), TensorSpec(n["k_up"], (H * d, rank)),
-                TensorSpec(n["v_up"], (H * dv, rank)), TensorSpec(n["o"], (h, H * dv))]
+        if params.get("q_rank") is None:
+            specs = [TensorSpec(n["q"], (H * (d + dr), h))]
+        else:
+            q_rank = int(params["q_rank"])
+            specs = [TensorSpec(n["q_down"], (q_rank, h)), TensorSpec(n["q_norm"], (q_rank,), kind="norm"),
+                     TensorSpec(n["q_up"], (H * (d + dr), q_rank))]
+        if not params.get("shared_cache"):
+            specs += [TensorSpec(n["kv_down"], (rank + dr, h)), TensorSpec(n["kv_norm"], (rank,), kind="norm")]
+        specs += [TensorSpec(n["k_up"], (H * d, rank)), TensorSpec(n["v_up"], (H * dv, rank))]
+        if params.get("gate"):
+            specs.append(TensorSpec(n["gate"], (H * dv, h)))
+        return specs + [TensorSpec(n["o"], (h, H * dv))]
 
     @staticmethod
     def cache_request(params):
@@ -207,21 +222,36 @@ class LatentAttention(Mixer):
         self.check_params(params)
         self.hidden, self.heads = int(params["hidden"]), int(params["heads"])
         self.d, self.dr, self.dv = int(params["head_dim"]), int(params["rot_dim"]), int(params["v_head_dim"])
-        self.rank, self.q_rank = int(params["kv_rank"]), int(params["q_rank"])
+        self.rank = int(params["kv_rank"])
+        self.q_rank = None if params.get("q_rank") is None else int(params["q_rank"])
         self.scale, self.window = float(params["scale"]), params.get("window")
         self.eps = float(params.get("norm_eps", 1e-6))
+        self.pairs, self.gated, self.own_cache = bool(params.get("rot_pairs")), bool(params.get("gate")), not params.get("shared_cache")
         n = self._names(params, prefix)
         H, d, dv, rank = self.heads, self.d, self.dv, self.rank
-        self.w_q_down = prepare_weight(tensors[n["q_down"]], runtime)
-        self.w_q_up = prepare_weight(tensors[n["q_up"]], runtime)
-        self.w_kv_down = prepare_weight(tensors[n["kv_down"]], runtime)
+        # One product for everything that is read from the input beside a query latent: [W_q (queries straight from the
+        # input) | W_dkv (a cache of the layer's own) | W_g (a gate)], padded with zero rows to a multiple of 8 columns.
+        blocks, at, self.columns = [], 0, {}
+        for key, present, rows in (("q", self.q_rank is None, H * (d + self.dr)), ("kv_down", self.own_cache, rank + self.dr),
+                                   ("gate", self.gated, H * dv)):
+            if present:
+                blocks.append(tensors[n[key]])
+                self.columns[key] = (at, at + rows)
+                at += rows
+        self.in_width = (at + 7) // 8 * 8
+        if self.in_width > at:
+            blocks.append(torch.zeros((self.in_width - at, self.hidden), dtype=blocks[0].dtype, device=blocks[0].device))
+        self.w_in = prepare_weight(torch.cat(blocks, dim=0), runtime) if at else None
+        if self.q_rank is not None:
+            self.w_q_down = prepare_weight(tensors[n["q_down"]], runtime)
+            self.w_q_up = prepare_weight(tensors[n["q_up"]], runtime)
+            norm_params = {"hidden": self.q_rank, "eps": self.eps, "tensor": ""}
+            self.q_norm = lookup(NORMS, "rmsnorm", "norm")(norm_params, {n["q_norm"]: tensors[n["q_norm"]]}, n["q_norm"], runtime)
         # head h's share of the key expansion, transposed: the product that takes a query into the latent's space
         self.w_k_up_t = prepare_weight(tensors[n["k_up"]].view(H, d, rank).transpose(1, 2), runtime)       # [H, rank, d]
         self.w_v_up = prepare_weight(tensors[n["v_up"]].view(H, dv, rank), runtime)                         # [H, dv, rank]
         self.w_o = prepare_weight(tensors[n["o"]], runtime)
-        norm_params = {"hidden": self.q_rank, "eps": self.eps, "tensor": ""}
-        self.q_norm = lookup(NORMS, "rmsnorm", "norm")(norm_params, {n["q_norm"]: tensors[n["q_norm"]]}, n["q_norm"], runtime)
-        self.kv_norm = tensors[n["kv_norm"]].to(torch.float32).contiguous()
+        self.kv_norm = tensors[n["kv_norm"]].to(torch.float32).contiguous() if self.own_cache else None
         self.rot_dims, self.freq = _frequencies(params.get("rot"), runtime.device)
         self.tensor_cores = runtime.compute_dtype == torch.bfloat16 and ops.latent_attention_accepts(self.rank, self.dr)
 
@@ -257,19 +287,26 @@ class LatentAttention(Mixer):
         rt, n = self.runtime, x.shape[0]
         H, d, dr, dv, rank = self.heads, self.d, self.dr, self.dv, self.rank
         flag, dtype = ctx.error_flag, rt.compute_dtype
-        q_latent = ctx.buffer("latent.cq", (n, self.q_rank), torch.float32)
-        linear(rt, STORE, x, self.w_q_down, q_latent, error_flag=flag, name="q_down")
-        shared = ctx.buffer("latent.shared", (n, rank + dr), torch.float32)
-        linear(rt, STORE, x, self.w_kv_down, shared, error_flag=flag, name="kv_down")
-        q_rows = ctx.buffer("latent.q", (n, H * (d + dr)), torch.float32)
-        linear(rt, STORE, DeferredNorm(ctx, self.q_norm, q_latent, buffer_name="latent.cq_normed"), self.w_q_up, q_rows,
-               error_flag=flag, name="q_up")
+        shared = gate = None
+        if self.w_in is not None:
+            rows = ctx.buffer("latent.in", (n, self.in_width), torch.float32)
+            linear(rt, STORE, x, self.w_in, rows, error_flag=flag, name="latent_in")
+            part = lambda key: rows[:, self.columns[key][0]:self.columns[key][1]] if key in self.columns else None
+            shared, gate = part("kv_down"), part("gate")
+        if self.q_rank is None:
+            q_rows = part("q")
+        else:
+            q_latent = ctx.buffer("latent.cq", (n, self.q_rank), torch.float32)
+            linear(rt, STORE, x, self.w_q_down, q_latent, error_flag=flag, name="q_down")
+            q_rows = ctx.buffer("latent.q", (n, H * (d + dr)), torch.float32)
+            linear(rt, STORE, DeferredNorm(ctx, self.q_norm, q_latent, buffer_name="latent.cq_normed"), self.w_q_up, q_rows,
+                   error_flag=flag, name="q_up")
         scratch = ctx.runtime.scratch
         q_plain = scratch("latent.q_plain", H * n * d, dtype).view(H, n, d)
         q_rotated = ctx.buffer("latent.q_rot", (n, H * dr), dtype)
         ops.latent_prepare(q_rows, shared, self.kv_norm, self.eps, self.freq, self.rot_dims, ctx.positions, ctx.slots,
-                           kv.block_table, q_plain, q_rotated, kv.k_pages, kv.v_pages, H, d, dr, rank, write_kv=kv.writes,
-                           error_flag=flag)
+                           kv.block_table, q_plain, q_rotated, kv.k_pages, kv.v_pages, H, d, dr, rank,
+                           write_kv=kv.writes and self.own_cache, error_flag=flag, pairs=self.pairs)
         q_absorbed = scratch("latent.q_absorbed", H * n * rank, dtype).view(H, n, rank)
         self._head_products(ctx, q_plain, self.w_k_up_t, q_absorbed, "k_up")
         mixed = scratch("latent.mixed", H * n * rank, dtype).view(H, n, rank)
@@ -286,4 +323,6 @@ class LatentAttention(Mixer):
                                   self.window, self.scale, sink=False, error_flag=flag)
         o = ctx.buffer("latent.o", (n, H * dv), dtype)
         self._head_products(ctx, mixed, self.w_v_up, o.view(n, H, dv).transpose(0, 1), "v_up")
+        if gate is not None:
+            ops.gate_rows(o, gate, ops.GATE_SIGMOID)
         linear(rt, STORE if store else ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")

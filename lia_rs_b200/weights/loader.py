@@ -41,7 +41,7 @@ class WeightError(ValueError):
 class TensorSpec:
     name: str
     shape: tuple
-    kind: str = "matrix"        # "matrix" (normal init) | "norm" (ones) | "table" (integers)
+    kind: str = "matrix"        # "matrix" (normal init) | "norm" (ones) | "identity" (a unit matrix) | "table" (integers)
     optional: bool = False
 
 

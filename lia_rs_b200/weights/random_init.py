@@ -20,6 +20,8 @@ def random_tensors(specs, seed: int, std: float) -> dict:
             continue
         if spec.kind == "norm":
             out[spec.name] = torch.ones(spec.shape, dtype=torch.bfloat16)
+        elif spec.kind == "identity":
+            out[spec.name] = torch.eye(spec.shape[0], spec.shape[1], dtype=torch.bfloat16)
         elif spec.kind == "table":
             out[spec.name] = torch.zeros(spec.shape, dtype=torch.int32)
         else:
