@@ -6,9 +6,9 @@
     streams         copies of the residual stream (hyper-connections); absent: one stream and plain residual sums
     logit_softcap   cap of the logits, cap * tanh(logits / cap); absent: none
     layers[]        type: which mixer the layer has; mixer: its sizes; mlp: its feed-forward, or null for none
-      "latent_attention"  mixer {heads, dim, rot_dim, vdim, kv_rank, scale, rot {base, dims}, kv_from (absent: the layer
-                                 has a cache of its own; j: it reads layer j's)}
-      "retention"         mixer {heads, dim, vdim, decay [one per head], rot {base, dims}}
+      "latent_attention"  mixer {heads, dim, rot_dim, vdim, kv_rank, scale, rot {base, dims} (absent: nothing turns),
+                                 kv_from (absent: the layer has a cache of its own; j: it reads layer j's)}
+      "retention"         mixer {heads, dim, vdim, decay [one per head], rot {base, dims} (absent: nothing turns)}
       mlp {kind "dense", ff}
       mlp {kind "moe", expert {ff}, router {experts, top, scale}, shared {ff} (absent: no shared expert)}
 
@@ -28,6 +28,8 @@ MLP_KINDS = ("dense", "moe")
 
 
 def _rot(mixer: dict, limit: int, where: str) -> None:
+    if mixer.get("rot") is None:                 # absent: nothing is rotated
+        return
     rot = _section(mixer, "rot", where)
     dims = _positive_int(rot.get("dims"), f"{where}.rot.dims")
     if dims % 2 or dims > limit:
@@ -96,7 +98,7 @@ class ZipelixConfig:
                     other = checked[source]
                     if other["type"] != "latent_attention" or other["mixer"].get("kv_from") is not None:
                         raise ConfigError(f"config.json: {where}.kv_from must name a latent-attention layer with a cache of its own")
-                    if any(other["mixer"][key] != mixer[key] for key in ("kv_rank", "rot_dim", "rot")):
+                    if any(other["mixer"].get(key) != mixer.get(key) for key in ("kv_rank", "rot_dim", "rot")):
                         raise ConfigError(f"config.json: {where}: kv_rank, rot_dim and rot must equal those of layer {source}")
             else:
                 decay = mixer.get("decay")

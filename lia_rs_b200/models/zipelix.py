@@ -27,14 +27,14 @@ def build_zipelix(config: ZipelixConfig) -> ModelSpec:
             source = m.get("kv_from")
             mixer = PartSpec("latent_attention", {
                 "hidden": width, "heads": m["heads"], "head_dim": m["dim"], "rot_dim": m["rot_dim"], "v_head_dim": m["vdim"],
-                "kv_rank": m["kv_rank"], "q_rank": None, "scale": m["scale"], "window": None, "norm_eps": eps, "rot": m["rot"],
+                "kv_rank": m["kv_rank"], "q_rank": None, "scale": m["scale"], "window": None, "norm_eps": eps, "rot": m.get("rot"),
                 "rot_pairs": True, "gate": "sigmoid", "shared_cache": source is not None})
             # a layer that reads another layer's latents uses that layer's cache and appends nothing
             schedule.append(ScheduleEntry(i, cache=i if source is None else int(source), writes=source is None))
         else:
             mixer = PartSpec("retention", {
                 "hidden": width, "heads": m["heads"], "head_dim": m["dim"], "v_head_dim": m["vdim"], "decay": list(m["decay"]),
-                "rot": m["rot"], "norm_eps": eps})
+                "rot": m.get("rot"), "norm_eps": eps})
             schedule.append(ScheduleEntry(i, cache=None))
         mlp = layer.get("mlp")
         if mlp is None:

@@ -69,7 +69,9 @@ def latent_cache(h, positions, w_dkv, w_norm, m, eps):
     rank, dr = m["kv_rank"], m["rot_dim"]
     both = h @ w_dkv.to(F64).T
     c = norm(both[:, :rank], w_norm, eps)
-    shared = rotate_interleaved(both[:, rank:rank + dr], positions, m["rot"]["base"], m["rot"]["dims"])
+    shared = both[:, rank:rank + dr]
+    if m.get("rot"):
+        shared = rotate_interleaved(shared, positions, m["rot"]["base"], m["rot"]["dims"])
     return c, shared
 
 
@@ -82,7 +84,9 @@ def latent_attention(h, positions, w, m, cache):
     c, shared = cache
     q = (h @ w["q"].to(F64).T).view(T, H, d + dr)
     q_plain = q[:, :, :d]
-    q_rot = rotate_interleaved(q[:, :, d:].contiguous(), positions, m["rot"]["base"], m["rot"]["dims"])
+    q_rot = q[:, :, d:].contiguous()
+    if m.get("rot"):
+        q_rot = rotate_interleaved(q_rot, positions, m["rot"]["base"], m["rot"]["dims"])
     k_plain = (c @ w["uk"].to(F64).T).view(T, H, d)
     v = (c @ w["uv"].to(F64).T).view(T, H, dv)
     scores = (torch.einsum("ihd,jhd->hij", q_plain, k_plain) + torch.einsum("ihd,jd->hij", q_rot, shared)) * float(m["scale"])
@@ -196,3 +200,15 @@ def forward(config: dict, tensors: dict, tokens, layer_outputs=None):
     if cap:
         logits = float(cap) * torch.tanh(logits / float(cap))
     return logits
+
+
+def greedy(config, weights, prompt, count):
+    """`count` tokens after `prompt`, each the largest logit's id (the largest id among equals)."""
+    tokens, out = list(prompt), []
+    for _ in range(count):
+        row = forward(config, weights, tokens)[-1]
+        best = row.max()
+        token = max(i for i in range(len(row)) if row[i] == best)
+        out.append(token)
+        tokens.append(token)
+    return out
