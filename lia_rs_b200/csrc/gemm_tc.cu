@@ -31,6 +31,11 @@
 // in the stream is still draining.  Weights do not depend on that kernel, so the first ring of W boxes
 // is requested at once; everything else waits at griddepcontrol.wait.
 //
+// Grouped products (a mixture of experts): W is [groups, n_total, K], the tokens' rows are sorted by group with every
+// group's rows beginning at a multiple of the tile's width, and a list on the device names each token tile's group,
+// first row and number of rows (csrc/moe.cu writes it).  A unit is then (token tile of the list, 128 features); the
+// list's length is read on the device, so the launch depends on the sizes alone.  K is not cut.
+//
 // Every wait on an mbarrier is bounded: when the bound is hit the role raises the error flag and leaves
 // its loop; the CTA then waits (bounded) for its copies in flight, frees its TMEM and returns.
 #include <algorithm>
@@ -68,19 +73,38 @@ struct Shape {
     float* partial;           // [splits][M][n_total]
     int* counters;            // [f_tiles * t_tiles], zero between launches
     int* error_flag;
+    const int* group_tiles;   // grouped: per token tile (group, first row, rows); nullptr: one matrix
+    const int* group_count;   // grouped: the number of token tiles
+    int group_rows;           // grouped: rows of W per group
 };
 
 // The k-th unit of this CTA: which tile, which K blocks.
 struct Unit {
     int f0, t0, tile, split, kb_begin, kb_end;
+    int w0;                   // the first row of W: f0, plus the group's first row
+    int t_end;                // tokens from here on are not the unit's
 };
 __device__ __forceinline__ Unit unit_at(const Shape& s, int index) {
     Unit u;
+    if (s.group_tiles) {
+        const int ft = index % s.f_tiles, tt = index / s.f_tiles;
+        u.tile = index;
+        u.split = 0;
+        u.f0 = ft * TILE_F;
+        u.t0 = s.group_tiles[3 * tt + 1];
+        u.t_end = u.t0 + s.group_tiles[3 * tt + 2];
+        u.w0 = s.group_tiles[3 * tt] * s.group_rows + u.f0;
+        u.kb_begin = 0;
+        u.kb_end = s.kblocks;
+        return u;
+    }
     u.tile = index / s.splits;
     u.split = index - u.tile * s.splits;
     const int ft = u.tile % s.f_tiles, tt = u.tile / s.f_tiles;
     u.f0 = ft * TILE_F;
     u.t0 = tt * s.n_tile;
+    u.w0 = u.f0;
+    u.t_end = s.M;
     u.kb_begin = (int)((long long)u.split * s.kblocks / s.splits);
     u.kb_end = (int)((long long)(u.split + 1) * s.kblocks / s.splits);
     return u;
@@ -109,7 +133,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // dynamic shared memory is aligned to 1024 bytes by hand (the swizzle pattern repeats every 1024)
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t staging_base = smem_base + (uint32_t)s.stages * stage_bytes;     // 2 x [32 tokens][128 features]
-    const int units = s.f_tiles * s.t_tiles * s.splits;
+    int units = s.f_tiles * s.t_tiles * s.splits;
     const int first_unit = blockIdx.x, stride = gridDim.x;
 
     if (warp == 0 && lane == 0) {
@@ -138,6 +162,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
     pdl_launch_dependents();
+    if (s.group_tiles) {
+        pdl_wait();           // the list of tiles is the work of a kernel ahead
+        units = min(*s.group_count, s.t_tiles) * s.f_tiles;
+    }
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer ----
@@ -145,7 +173,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // weights do not depend on it.  X does, so its boxes wait.
         bool ok = true;
         int issued = 0, ahead = 0;
-        {
+        if (!s.group_tiles) {
             int it = 0;
             for (int index = first_unit; index < units && it < s.stages; index += stride) {
                 const Unit u = unit_at(s, index);
@@ -153,8 +181,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     const uint32_t full = smem_u32(&full_bar[it]);
                     const uint32_t dst = smem_base + (uint32_t)it * stage_bytes;
                     mbar_expect_tx(full, stage_bytes);
-                    tma_load_2d(dst, &map_w, kb * BLOCK_K, u.f0, full);
-                    if (A_TILES == 2) tma_load_2d(dst + a_bytes, &map_w, kb * BLOCK_K, s.N + u.f0, full);
+                    tma_load_2d(dst, &map_w, kb * BLOCK_K, u.w0, full);
+                    if (A_TILES == 2) tma_load_2d(dst + a_bytes, &map_w, kb * BLOCK_K, s.N + u.w0, full);
                 }
             }
             ahead = it;
@@ -172,8 +200,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (it >= ahead) {
                     if (!mbar_wait(smem_u32(&empty_bar[st]), phase ^ 1u)) { ok = false; break; }
                     mbar_expect_tx(full, stage_bytes);
-                    tma_load_2d(dst, &map_w, kb * BLOCK_K, u.f0, full);
-                    if (A_TILES == 2) tma_load_2d(dst + a_bytes, &map_w, kb * BLOCK_K, s.N + u.f0, full);
+                    tma_load_2d(dst, &map_w, kb * BLOCK_K, u.w0, full);
+                    if (A_TILES == 2) tma_load_2d(dst + a_bytes, &map_w, kb * BLOCK_K, s.N + u.w0, full);
                 }
                 tma_load_2d(dst + A_TILES * a_bytes, &map_x, kb * BLOCK_K, u.t0, full);
                 if (s.x_box < s.n_tile)
@@ -324,7 +352,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             } else if (s.via_tma) {
                 // through shared memory, 32 tokens at a time, out by TMA
                 for (int c0 = 0; c0 < s.n_tile; c0 += STAGING_TOKENS) {
-                    if (u.t0 + c0 >= s.M) break;
+                    if (u.t0 + c0 >= u.t_end) break;
                     float acc[32], up[32];
                     tmem_load32_nowait(lane_addr + (uint32_t)c0, acc);
                     if (MODE == GEMM_SWIGLU) tmem_load32_nowait(lane_addr + (uint32_t)(s.n_tile + c0), up);
@@ -357,7 +385,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
             } else {
                 for (int c0 = 0; c0 < s.n_tile; c0 += 16) {
-                    if (u.t0 + c0 >= s.M) break;                    // uniform over the warp
+                    if (u.t0 + c0 >= u.t_end) break;                // uniform over the warp
                     float acc[16], up[16];
                     tmem_load16(lane_addr + (uint32_t)c0, acc);
                     if (MODE == GEMM_SWIGLU) tmem_load16(lane_addr + (uint32_t)(s.n_tile + c0), up);
@@ -365,7 +393,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
                             const int t = u.t0 + c0 + c;
-                            if (t >= s.M) break;
+                            if (t >= u.t_end) break;
                             apply_epilogue<MODE, TO>(out + (size_t)t * s.ldo + f, acc[c], up[c], s.alpha);
                         }
                     }
@@ -491,6 +519,7 @@ LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int 
     s.acc_buffers = 2 * s.acc_cols <= 512 ? 2 : 1;
     s.tmem_cols = pow2_at_least(s.acc_buffers * s.acc_cols);
     s.ldo = ldo; s.alpha = alpha; s.error_flag = error_flag;
+    s.group_tiles = nullptr; s.group_count = nullptr; s.group_rows = 0;
     s.counters = reinterpret_cast<int*>(scratch);
     s.partial = scratch ? scratch + COUNTER_WORDS : nullptr;
     const int esize = out_dtype == LIA_F32 ? 4 : 2;
@@ -514,6 +543,56 @@ LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int 
     if (mode == GEMM_STORE && out_dtype == LIA_F32) return launch<GEMM_STORE, float>(mw, mx, mo, (float*)out, s, grid, stream);
     if (mode == GEMM_STORE) return launch<GEMM_STORE, __nv_bfloat16>(mw, mx, mo, (__nv_bfloat16*)out, s, grid, stream);
     if (mode == GEMM_ACCUM) return launch<GEMM_ACCUM, float>(mw, mx, mo, (float*)out, s, grid, stream);
+    if (out_dtype == LIA_F32) return launch<GEMM_SWIGLU, float>(mw, mx, mo, (float*)out, s, grid, stream);
+    return launch<GEMM_SWIGLU, __nv_bfloat16>(mw, mx, mo, (__nv_bfloat16*)out, s, grid, stream);
+}
+
+// The grouped product: X [rows_cap, K] bf16 = the tokens' rows sorted by group, every group's rows beginning at a multiple
+// of n_tile; W [groups, n_total, K] bf16 (n_total = N, or 2N for SWIGLU: gate rows then up rows); out [rows_cap, N].
+// `tiles` [3 * max_tiles] on the device lists (group, first row, rows) per token tile and `n_tiles` [1] how many there
+// are; rows of X and out that belong to no tile's rows are read and may be written (with what their X rows give).
+// n_tile: 16, 32, 64, 128, or 256 for the ungated modes.  GEMM_STORE or GEMM_SWIGLU.
+LIA_EXPORT int lia_gemm_tc_grouped(int mode, const void* X, int ldx, int rows_cap, const void* W, int ldw, int groups,
+                                   void* out, int out_dtype, int ldo, int N, int K, int n_tile, const int* tiles,
+                                   const int* n_tiles, int max_tiles, int sm_count, int* error_flag, cudaStream_t stream) {
+    if (rows_cap <= 0 || N <= 0 || max_tiles <= 0) return LIA_OK;
+    if (K <= 0 || K % 8 || ldx < K || ldw < K || ldo < N || sm_count <= 0 || groups <= 0 || !tiles || !n_tiles) return LIA_ERR_SIZE;
+    if (mode != GEMM_STORE && mode != GEMM_SWIGLU) return LIA_ERR_SIZE;
+    if (out_dtype != LIA_F32 && out_dtype != LIA_BF16) return LIA_ERR_DTYPE;
+    const bool swiglu = mode == GEMM_SWIGLU;
+    if (n_tile < 16 || n_tile > (swiglu ? 128 : 256) || (n_tile & (n_tile - 1)) || (long long)max_tiles * n_tile > rows_cap)
+        return LIA_ERR_SIZE;
+    Shape s;
+    s.M = rows_cap; s.N = N; s.K = K; s.n_total = swiglu ? 2 * N : N;
+    s.n_tile = n_tile; s.splits = 1; s.f_tiles = (N + TILE_F - 1) / TILE_F; s.t_tiles = max_tiles;
+    s.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+    s.x_box = n_tile;
+    s.acc_cols = swiglu ? 2 * n_tile : n_tile;
+    s.acc_buffers = 2;
+    s.tmem_cols = pow2_at_least(2 * s.acc_cols);
+    s.ldo = ldo; s.alpha = 1.0f; s.error_flag = error_flag;
+    s.counters = nullptr; s.partial = nullptr;
+    s.group_tiles = tiles; s.group_count = n_tiles; s.group_rows = s.n_total;
+    const int esize = out_dtype == LIA_F32 ? 4 : 2;
+    s.via_tma = (n_tile >= 64 && ((uintptr_t)out & 15u) == 0 && ((long long)ldo * esize) % 16 == 0) ? 1 : 0;
+    const int staging = s.via_tma ? 2 * STAGING_TOKENS * TILE_F * esize : 0;
+    const int stage_bytes = (swiglu ? 2 : 1) * TILE_F * BLOCK_K * 2 + n_tile * BLOCK_K * 2;
+    s.stages = max(2, min(MAX_STAGES, (SMEM_BYTES - 1024 - staging) / stage_bytes));
+
+    CUtensorMap mw, mx, mo;
+    int rc;
+    if ((long long)groups * s.n_total > 0x7fffffffLL) return LIA_ERR_SIZE;
+    if ((rc = make_map(&mw, W, groups * s.n_total, K, ldw, TILE_F)) != LIA_OK) return rc;
+    if ((rc = make_map(&mx, X, rows_cap, K, ldx, s.x_box)) != LIA_OK) return rc;
+    if (s.via_tma) {
+        if ((rc = make_out_map(&mo, out, out_dtype, rows_cap, N, ldo, STAGING_TOKENS)) != LIA_OK) return rc;
+    } else {
+        mo = mx;
+    }
+    const long long units = (long long)s.f_tiles * max_tiles;
+    const int grid = (int)min((long long)sm_count, units);
+    if (mode == GEMM_STORE && out_dtype == LIA_F32) return launch<GEMM_STORE, float>(mw, mx, mo, (float*)out, s, grid, stream);
+    if (mode == GEMM_STORE) return launch<GEMM_STORE, __nv_bfloat16>(mw, mx, mo, (__nv_bfloat16*)out, s, grid, stream);
     if (out_dtype == LIA_F32) return launch<GEMM_SWIGLU, float>(mw, mx, mo, (float*)out, s, grid, stream);
     return launch<GEMM_SWIGLU, __nv_bfloat16>(mw, mx, mo, (__nv_bfloat16*)out, s, grid, stream);
 }

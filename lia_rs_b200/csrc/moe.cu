@@ -5,11 +5,15 @@
 //    an optional extra row of the router matrix gives one more logit a token, whose logistic function is the gate of a
 //    shared expert.
 //  * `moe_plan`: the (token, choice) pairs grouped by expert: where each expert's rows begin, which pair each sorted row
-//    is, where each pair went, and the list of (expert, first row) tiles of TILE_M rows that the products run over.
+//    is, where each pair went, and the list of (expert, first row, rows) tiles of `tile_rows` rows that the products run
+//    over.  With `pad` every expert's group begins at a multiple of `tile_rows` (rows in between belong to no pair), so
+//    that a tile of the tensor-core product (csrc/gemm_tc.cu, grouped) never holds rows of two experts.
 //    Which pair gets which row inside an expert's group is not fixed, and does not matter: every row of a product is
 //    computed for itself, its sum over K in ascending order.
-//  * `moe_gemm`: for every tile, rows x W_e^T with the expert's own matrix: `MODE_GATE_UP` reads token rows through the
-//    sorted list and writes up * silu(gate) of [W_gate; W_up]; `MODE_DOWN` reads the sorted rows and writes 32-bit rows.
+//  * `moe_gather`: the sorted rows' inputs side by side (rows of no pair are zero), for the tensor-core product.
+//  * `moe_gemm`: for every tile, rows x W_e^T with the expert's own matrix, on the 32-bit pipes (the 32-bit path, and
+//    sizes that TMA cannot address): `MODE_GATE_UP` reads token rows through the sorted list and writes up * silu(gate)
+//    of [W_gate; W_up]; `MODE_DOWN` reads the sorted rows and writes 32-bit rows.
 //  * `moe_combine`: residual (+)= alpha * (sum_c weight_c y[row of (t, c)] + gate_t shared_t), the choices added in
 //    their order, so a token's result does not depend on what else is in the batch.
 #include "common.cuh"
@@ -61,13 +65,15 @@ __global__ void moe_route_kernel(const T* __restrict__ x, long long ld, const fl
     if (extra) shared_gate[t] = 1.0f / (1.0f + expf(-z[experts]));
 }
 
-__global__ void moe_plan_kernel(const int* __restrict__ ids, int pairs, int experts, int* __restrict__ offsets,
-                                int* __restrict__ order, int* __restrict__ inverse, int* __restrict__ tiles,
-                                int* __restrict__ n_tiles) {
+__global__ void moe_plan_kernel(const int* __restrict__ ids, int pairs, int experts, int tile_rows, int pad, int rows_cap,
+                                int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ inverse,
+                                int* __restrict__ tiles, int* __restrict__ n_tiles) {
     __shared__ int counts[MOE_MAX_EXPERTS], starts[MOE_MAX_EXPERTS + 1], tile_starts[MOE_MAX_EXPERTS + 1];
     pdl_launch_dependents();
     pdl_wait();
     for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+    if (pad)
+        for (int r = threadIdx.x; r < rows_cap; r += blockDim.x) order[r] = -1;
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = ids[p];
@@ -77,10 +83,11 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, int pairs, int expe
     if (threadIdx.x == 0) {
         int at = 0, tile = 0;
         for (int e = 0; e < experts; ++e) {
+            if (pad) at = tile * tile_rows;
             starts[e] = at;
             tile_starts[e] = tile;
             at += counts[e];
-            tile += (counts[e] + TILE_M - 1) / TILE_M;
+            tile += (counts[e] + tile_rows - 1) / tile_rows;
         }
         starts[experts] = at;
         tile_starts[experts] = tile;
@@ -90,11 +97,14 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, int pairs, int expe
     for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = starts[e];
     for (int e = threadIdx.x; e < experts; e += blockDim.x) {
         for (int k = tile_starts[e]; k < tile_starts[e + 1]; ++k) {
-            tiles[2 * k] = e;
-            tiles[2 * k + 1] = starts[e] + (k - tile_starts[e]) * TILE_M;
+            const int first = (k - tile_starts[e]) * tile_rows;
+            tiles[3 * k] = e;
+            tiles[3 * k + 1] = starts[e] + first;
+            tiles[3 * k + 2] = min(tile_rows, counts[e] - first);
         }
-        counts[e] = 0;                                     // (only this thread touched counts[e] since the barrier)
     }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = ids[p];
@@ -105,20 +115,30 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, int pairs, int expe
     }
 }
 
+// dst[r] = src[order[r] / top] (zero where order[r] < 0); rows of `width` elements, a multiple of 8.
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ src, long long ld, const int* __restrict__ order, int top,
+                                  __nv_bfloat16* __restrict__ dst, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int p = order[blockIdx.x];
+    const uint4* from = p >= 0 ? reinterpret_cast<const uint4*>(src + (size_t)(p / top) * ld) : nullptr;
+    uint4* to = reinterpret_cast<uint4*>(dst + (size_t)blockIdx.x * width);
+    for (int i = threadIdx.x; i < width / 8; i += blockDim.x) to[i] = from ? from[i] : make_uint4(0, 0, 0, 0);
+}
+
 // MODE 0: out[r, n] = sum_k a[r, k] w_e[n, k] (32-bit out).  MODE 1: out[r, n] = u * silu(g), g = a . w_e[n], u = a . w_e[N + n].
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const T* __restrict__ a, long long lda, const int* __restrict__ order, int top,
                 const T* __restrict__ w, long long expert_stride, void* __restrict__ out_raw, long long ldo,
-                const int* __restrict__ offsets, const int* __restrict__ tiles, const int* __restrict__ n_tiles, int N, int K) {
+                const int* __restrict__ tiles, const int* __restrict__ n_tiles, int N, int K) {
     __shared__ float as[TILE_K][TILE_M + 1];
     __shared__ __align__(16) float ws[MODE == 1 ? 2 : 1][TILE_K][TILE_N];
     __shared__ int source[TILE_M];
     pdl_launch_dependents();
     pdl_wait();
     if ((int)blockIdx.x >= *n_tiles) return;
-    const int e = tiles[2 * blockIdx.x], row0 = tiles[2 * blockIdx.x + 1];
-    const int rows = min(TILE_M, offsets[e + 1] - row0);
+    const int e = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
     const int n0 = blockIdx.y * TILE_N;
     const T* we = w + (size_t)e * expert_stride;
     if (threadIdx.x < TILE_M) {
@@ -229,21 +249,34 @@ LIA_EXPORT int lia_moe_route(const void* x, int dtype, long long ld, const float
     return LIA_ERR_DTYPE;
 }
 
-// ids [pairs]; offsets [experts + 1]; order, inverse [pairs]; tiles [2 * (pairs / TILE_M + experts)]; n_tiles [1].
-LIA_EXPORT int lia_moe_plan(const int* ids, int pairs, int experts, int* offsets, int* order, int* inverse, int* tiles,
-                            int* n_tiles, cudaStream_t stream) {
+// ids [pairs]; offsets [experts + 1]; order [pairs, or rows_cap with pad]; inverse [pairs]; tiles [3 * (pairs / tile_rows +
+// min(experts, pairs))]; n_tiles [1].  pad: every expert's rows begin at a multiple of tile_rows, and `order` is -1 on the
+// rows of no pair, up to rows_cap = tile_rows * the most tiles.
+LIA_EXPORT int lia_moe_plan(const int* ids, int pairs, int experts, int tile_rows, int pad, int rows_cap, int* offsets,
+                            int* order, int* inverse, int* tiles, int* n_tiles, cudaStream_t stream) {
     if (pairs <= 0) return LIA_OK;
-    if (experts <= 0 || experts > MOE_MAX_EXPERTS) return LIA_ERR_SIZE;
-    return lia_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, ids, pairs, experts, offsets, order, inverse, tiles,
-                      n_tiles);
+    if (experts <= 0 || experts > MOE_MAX_EXPERTS || tile_rows <= 0) return LIA_ERR_SIZE;
+    if (pad && rows_cap < (pairs / tile_rows + min(experts, pairs)) * tile_rows) return LIA_ERR_SIZE;
+    return lia_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, ids, pairs, experts, tile_rows, pad, rows_cap, offsets,
+                      order, inverse, tiles, n_tiles);
+}
+
+// dst [rows, width] bf16 = src[order[r] / top] (zero where order[r] < 0); width a multiple of 8, 16-byte aligned rows.
+LIA_EXPORT int lia_moe_gather(const void* src, long long ld, const int* order, int top, void* dst, int rows, int width,
+                              cudaStream_t stream) {
+    if (rows <= 0) return LIA_OK;
+    if (width <= 0 || width % 8 || ld % 8 || top <= 0) return LIA_ERR_SIZE;
+    if (((uintptr_t)src & 15u) || ((uintptr_t)dst & 15u)) return LIA_ERR_ALIGN;
+    return lia_launch(moe_gather_kernel, dim3(rows), dim3(width >= 2048 ? 256 : 128), 0, stream, (const __nv_bfloat16*)src, ld,
+                      order, top, (__nv_bfloat16*)dst, width);
 }
 
 // mode 1: a = the tokens' rows [n, lda] read through `order` (pair -> token pair / top), w [experts, 2 N, K], out
 // [pairs, ldo] of `dtype`.  mode 0: a = sorted rows [pairs, lda], w [experts, N, K], out [pairs, ldo] 32-bit.
-// `max_tiles`: pairs / TILE_M + min(experts, pairs), the most tiles the plan can list.
+// `max_tiles`: pairs / TILE_M + min(experts, pairs), the most tiles the plan can list (planned with TILE_M rows a tile).
 LIA_EXPORT int lia_moe_gemm(int mode, const void* a, int dtype, long long lda, const int* order, int top, const void* w,
-                            void* out, long long ldo, const int* offsets, const int* tiles, const int* n_tiles,
-                            int max_tiles, int N, int K, cudaStream_t stream) {
+                            void* out, long long ldo, const int* tiles, const int* n_tiles, int max_tiles, int N, int K,
+                            cudaStream_t stream) {
     if (max_tiles <= 0) return LIA_OK;
     if (N <= 0 || K <= 0 || lda < K || ldo < N || top <= 0 || (mode != 0 && mode != 1) || (mode == 1 && !order))
         return LIA_ERR_SIZE;
@@ -251,7 +284,7 @@ LIA_EXPORT int lia_moe_gemm(int mode, const void* a, int dtype, long long lda, c
     const long long stride = (long long)(mode == 1 ? 2 : 1) * N * K;
 #define LIA_MOE(T, MODE)                                                                                              \
     return lia_launch(moe_gemm_kernel<T, MODE>, grid, dim3(256), 0, stream, (const T*)a, lda, order, top, (const T*)w, \
-                      stride, out, ldo, offsets, tiles, n_tiles, N, K)
+                      stride, out, ldo, tiles, n_tiles, N, K)
     if (dtype == LIA_F32) {
         if (mode == 1) LIA_MOE(float, 1);
         LIA_MOE(float, 0);

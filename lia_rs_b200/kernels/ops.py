@@ -129,9 +129,12 @@ class _Signatures:
     lia_moe_tile_rows = []
     lia_moe_route = [c_void_p, c_int, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                      c_void_p, c_void_p, c_void_p]
-    lia_moe_plan = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+    lia_moe_plan = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+    lia_moe_gather = [c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
     lia_moe_gemm = [c_int, c_void_p, c_int, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong,
-                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+                    c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lia_gemm_tc_grouped = [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                           c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
     lia_moe_combine = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int,
                        c_void_p]
     lia_retention_chunks = [c_int, c_int]
@@ -1142,9 +1145,28 @@ def moe_tile_rows() -> int:
     return int(lib().lia_moe_tile_rows())
 
 
-def moe_max_tiles(pairs: int, experts: int) -> int:
-    """The most row tiles that `pairs` (token, choice) pairs grouped by expert can be cut into."""
-    return pairs // moe_tile_rows() + min(experts, pairs)
+def moe_max_tiles(pairs: int, experts: int, tile_rows: int = 0) -> int:
+    """The most row tiles of `tile_rows` rows (0: the 32-bit product's) that `pairs` (token, choice) pairs grouped by expert
+    can be cut into."""
+    return pairs // (tile_rows or moe_tile_rows()) + min(experts, pairs)
+
+
+def moe_grouped_tile_rows(pairs: int, experts: int) -> int:
+    """Tokens per tile of the tensor-core product over the experts: the power of two from 16 to 128 that holds an expert's
+    share of evenly spread pairs (a function of the step's numbers alone)."""
+    rows = 16
+    while rows < 128 and rows * experts < pairs:
+        rows *= 2
+    return rows
+
+
+def moe_grouped_accepts(x, w_gate_up, w_down) -> bool:
+    """Whether the tensor-core product takes the experts' matrices: bfloat16, both reduction lengths multiples of 8
+    elements, 16-byte aligned bases (what TMA can address)."""
+    return (x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and w_gate_up.shape[2] % 8 == 0 and
+            w_down.shape[2] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1 and x.data_ptr() % 16 == 0 and
+            w_gate_up.is_contiguous() and w_down.is_contiguous() and w_gate_up.data_ptr() % 16 == 0 and
+            w_down.data_ptr() % 16 == 0)
 
 
 def moe_route(x, router, top: int, scale: float, ids, weights, shared_gate=None):
@@ -1162,23 +1184,39 @@ def moe_route(x, router, top: int, scale: float, ids, weights, shared_gate=None)
                                    float(scale), extra, _p(ids), _p(weights), _p(shared_gate), _stream()), "moe_route")
 
 
-def moe_plan(ids, experts: int, offsets, order, inverse, tiles, n_tiles):
-    """The pairs grouped by expert: offsets [experts + 1], order and inverse [pairs], the tile list and its length."""
+def moe_plan(ids, experts: int, offsets, order, inverse, tiles, n_tiles, tile_rows: int = 0, pad: bool = False):
+    """The pairs grouped by expert: offsets [experts + 1], order (which pair a sorted row is) and inverse [pairs], the list
+    of (expert, first row, rows) tiles of `tile_rows` rows (0: the 32-bit product's) and its length.  `pad`: every
+    expert's rows begin at a multiple of tile_rows; `order` then has tile_rows * the most tiles entries, -1 on the rows
+    of no pair."""
     _cuda(ids, offsets, order, inverse, tiles, n_tiles)
     pairs = ids.numel()
-    if offsets.numel() < experts + 1 or order.numel() < pairs or inverse.numel() < pairs or \
-            tiles.numel() < 2 * moe_max_tiles(pairs, experts):
+    tile_rows = tile_rows or moe_tile_rows()
+    most = moe_max_tiles(pairs, experts, tile_rows)
+    if offsets.numel() < experts + 1 or order.numel() < (most * tile_rows if pad else pairs) or inverse.numel() < pairs or \
+            tiles.numel() < 3 * most:
         raise KernelError("moe_plan: a list is too short")
     with _timed("moe_plan"):
-        _check(lib().lia_moe_plan(_p(ids), pairs, int(experts), _p(offsets), _p(order), _p(inverse), _p(tiles), _p(n_tiles),
-                                  _stream()), "moe_plan")
+        _check(lib().lia_moe_plan(_p(ids), pairs, int(experts), int(tile_rows), 1 if pad else 0, order.numel(), _p(offsets),
+                                  _p(order), _p(inverse), _p(tiles), _p(n_tiles), _stream()), "moe_plan")
 
 
-def moe_gemm(gated: bool, a, order, top: int, w, out, offsets, tiles, n_tiles, max_tiles: int, label=None):
-    """The experts' products over the planned tiles.  `gated`: a = the tokens' rows, read through `order`; w [experts,
-    2 N, K] = [gate; up]; out [pairs, N] = up * silu(gate) in the compute element type.  Else a = sorted rows [pairs, K],
-    w [experts, N, K], out [pairs, N] 32-bit."""
-    _cuda(a, order, w, out, offsets, tiles, n_tiles)
+def moe_gather(x, order, top: int, out):
+    """out[r] = x[order[r] / top], zero where order[r] < 0: the sorted rows' inputs side by side (bfloat16)."""
+    _cuda(x, order, out)
+    if x.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or out.shape[1] != x.shape[1] or not out.is_contiguous() or \
+            order.numel() < out.shape[0] or x.stride(1) != 1:
+        raise KernelError("moe_gather: shapes or element types do not agree")
+    with _timed("moe_gather"):
+        _check(lib().lia_moe_gather(_p(x), x.stride(0), _p(order), int(top), _p(out), out.shape[0], out.shape[1], _stream()),
+               "moe_gather")
+
+
+def moe_gemm(gated: bool, a, order, top: int, w, out, tiles, n_tiles, max_tiles: int, label=None):
+    """The experts' products over the planned tiles, on the 32-bit pipes.  `gated`: a = the tokens' rows, read through
+    `order`; w [experts, 2 N, K] = [gate; up]; out [pairs, N] = up * silu(gate) in the compute element type.  Else a =
+    sorted rows [pairs, K], w [experts, N, K], out [pairs, N] 32-bit."""
+    _cuda(a, order, w, out, tiles, n_tiles)
     N, K = out.shape[1], a.shape[1]
     if w.dim() != 3 or w.shape[1] != (2 * N if gated else N) or w.shape[2] != K or a.dtype != w.dtype or \
             out.dtype != (a.dtype if gated else torch.float32):
@@ -1186,8 +1224,24 @@ def moe_gemm(gated: bool, a, order, top: int, w, out, offsets, tiles, n_tiles, m
     pairs = out.shape[0]
     with _timed("moe_gemm", label, nbytes=w.numel() * w.element_size(), flops=2 * pairs * w.shape[1] * K):
         _check(lib().lia_moe_gemm(1 if gated else 0, _p(a), dtype_code(a.dtype), a.stride(0), _p(order), int(top), _p(w),
-                                  _p(out), out.stride(0), _p(offsets), _p(tiles), _p(n_tiles), int(max_tiles), N, K,
-                                  _stream()), "moe_gemm")
+                                  _p(out), out.stride(0), _p(tiles), _p(n_tiles), int(max_tiles), N, K, _stream()), "moe_gemm")
+
+
+def gemm_tc_grouped(mode, a, w, out, tile_rows: int, tiles, n_tiles, max_tiles: int, pairs: int, error_flag=None, label=None):
+    """out[r] = a[r] @ w[e(r)]^T on the tensor cores, rows sorted and padded by expert as `moe_plan(pad=True)` lists them:
+    a [rows, K] bfloat16, w [experts, N or 2 N, K] bfloat16, out [rows, N]; GEMM_STORE or GEMM_SWIGLU (csrc/gemm_tc.cu).
+    `pairs`: the rows that belong to a pair (for the profile's count of the work)."""
+    _cuda(a, w, out, tiles, n_tiles)
+    rows, K = a.shape
+    N = out.shape[1]
+    if w.dim() != 3 or w.shape[1] != (2 * N if mode == GEMM_SWIGLU else N) or w.shape[2] != K or out.shape[0] != rows or \
+            not w.is_contiguous():
+        raise KernelError("gemm_tc_grouped: shapes do not agree")
+    _, sms = _device_scratch(a.device)
+    with _timed("gemm_tc_grouped", label, nbytes=w.numel() * w.element_size(), flops=2 * pairs * w.shape[1] * K):
+        _check(lib().lia_gemm_tc_grouped(mode, _p(a), a.stride(0), rows, _p(w), K, w.shape[0], _p(out), dtype_code(out.dtype),
+                                         out.stride(0), N, K, int(tile_rows), _p(tiles), _p(n_tiles), int(max_tiles), sms,
+                                         _p(error_flag), _stream()), "gemm_tc_grouped")
 
 
 def moe_combine(residual, y, inverse, weights, shared_y, shared_gate, top: int, alpha: float, store: bool):

@@ -8,8 +8,10 @@
 
 `shared` (optional) is one more expert of a size of its own that every token uses, times a gate of one number per token.
 The router's product, the softmax, the choice and the weights are 32-bit; the (token, choice) pairs are grouped by expert
-on the device, each expert's rows go through its two products in tiles, and one kernel adds a token's weighted rows, in
-the order of its choices, into the residual stream (csrc/moe.cu).  Nothing is decided on the host, so a step's launches
+on the device, each expert's rows go through its two products in tiles (bfloat16: the grouped product on the tensor
+cores, csrc/gemm_tc.cu, over rows padded to whole tiles per expert; 32-bit, and sizes that TMA cannot address: the
+product on the 32-bit pipes), and one kernel adds a token's weighted rows, in the order of its choices, into the
+residual stream (csrc/moe.cu).  Nothing is decided on the host, so a step's launches
 depend on its number of tokens alone, and a token's result does not depend on what else is in the batch.
 
 Parameters: hidden, experts, top, intermediate, router_scale, shared ({"intermediate": n} or None), and optionally
@@ -81,6 +83,7 @@ class ExpertMixture(FeedForward):
             self.w_shared_gate_up = prepare_weight(torch.cat([tensors[p + n["gate"]], tensors[p + n["up"]]], dim=0), runtime)
             self.w_shared_down = prepare_weight(tensors[p + n["down"]], runtime)
         self.router = torch.cat(router, dim=0).to(torch.float32).contiguous()
+        self.grouped = None          # whether the tensor-core product takes the experts' matrices: known at the first step
 
     def forward(self, ctx, x, residual, scale, store=False):
         rt, n = self.runtime, x.shape[0]
@@ -91,16 +94,32 @@ class ExpertMixture(FeedForward):
         weights = scratch("moe.weights", pairs, torch.float32).view(n, top)
         shared_gate = scratch("moe.shared_gate", n, torch.float32) if self.shared else None
         ops.moe_route(x, self.router, top, self.router_scale, ids, weights, shared_gate)
-        max_tiles = ops.moe_max_tiles(pairs, experts)
-        lists = scratch("moe.lists", experts + 2 + 2 * pairs + 2 * max_tiles, torch.int32)
+        if self.grouped is None:
+            self.grouped = ops.moe_grouped_accepts(x, self.w_gate_up, self.w_down)
+        if self.grouped:
+            # the tensor cores: every expert's rows begin at a multiple of the tile, the rows' inputs are laid side by side
+            tile_rows = ops.moe_grouped_tile_rows(pairs, experts)
+            max_tiles = ops.moe_max_tiles(pairs, experts, tile_rows)
+            rows = max_tiles * tile_rows
+        else:
+            tile_rows, max_tiles, rows = 0, ops.moe_max_tiles(pairs, experts), pairs
+        lists = scratch("moe.lists", experts + 2 + rows + pairs + 3 * max_tiles, torch.int32)
         offsets, n_tiles = lists[:experts + 1], lists[experts + 1:experts + 2]
-        order, inverse = lists[experts + 2:experts + 2 + pairs], lists[experts + 2 + pairs:experts + 2 + 2 * pairs]
-        tiles = lists[experts + 2 + 2 * pairs:]
-        ops.moe_plan(ids.view(-1), experts, offsets, order, inverse, tiles, n_tiles)
-        act = scratch("moe.act", pairs * self.ff, dtype).view(pairs, self.ff)
-        ops.moe_gemm(True, x, order, top, self.w_gate_up, act, offsets, tiles, n_tiles, max_tiles, label="gate_up")
-        y = scratch("moe.y", pairs * self.hidden, torch.float32).view(pairs, self.hidden)
-        ops.moe_gemm(False, act, None, top, self.w_down, y, offsets, tiles, n_tiles, max_tiles, label="down")
+        order, inverse = lists[experts + 2:experts + 2 + rows], lists[experts + 2 + rows:experts + 2 + rows + pairs]
+        tiles = lists[experts + 2 + rows + pairs:]
+        ops.moe_plan(ids.view(-1), experts, offsets, order, inverse, tiles, n_tiles, tile_rows, pad=self.grouped)
+        act = scratch("moe.act", rows * self.ff, dtype).view(rows, self.ff)
+        y = scratch("moe.y", rows * self.hidden, torch.float32).view(rows, self.hidden)
+        if self.grouped:
+            sorted_x = scratch("moe.x", rows * self.hidden, dtype).view(rows, self.hidden)
+            ops.moe_gather(x, order, top, sorted_x)
+            ops.gemm_tc_grouped(SWIGLU, sorted_x, self.w_gate_up, act, tile_rows, tiles, n_tiles, max_tiles, pairs,
+                                error_flag=ctx.error_flag, label="gate_up")
+            ops.gemm_tc_grouped(STORE, act, self.w_down, y, tile_rows, tiles, n_tiles, max_tiles, pairs,
+                                error_flag=ctx.error_flag, label="down")
+        else:
+            ops.moe_gemm(True, x, order, top, self.w_gate_up, act, tiles, n_tiles, max_tiles, label="gate_up")
+            ops.moe_gemm(False, act, None, top, self.w_down, y, tiles, n_tiles, max_tiles, label="down")
         shared_y = None
         if self.shared:
             shared_act = ctx.buffer("moe.shared_act", (n, self.ffs), dtype)
