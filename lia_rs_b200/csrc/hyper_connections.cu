@@ -105,6 +105,107 @@ __global__ void hyper_step_kernel(float* __restrict__ x, const float* __restrict
         nr[i] = from_float<TO>(ur[i] * inv * norm_w[i]);
 }
 
+// The same step four elements at a time: hidden a multiple of 4, every row 16-byte aligned, at most VEC_ITERS * blockDim
+// groups of four a row, so that a thread keeps its part of u in registers between the sum and the norm.
+constexpr int VEC_ITERS = 4;
+
+__device__ __forceinline__ float4 fma4(float a, float4 b, float4 c) {
+    return make_float4(fmaf(a, b.x, c.x), fmaf(a, b.y, c.y), fmaf(a, b.z, c.z), fmaf(a, b.w, c.w));
+}
+__device__ __forceinline__ void store4(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(512) hyper_step_vec_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ mix,
+                                      const float* __restrict__ out_w, const float* __restrict__ in_w,
+                                      const int* __restrict__ rows_index, float* __restrict__ u,
+                                      const float* __restrict__ norm_w, TO* __restrict__ normed, int rows, int hidden,
+                                      int streams, float eps) {
+    __shared__ float coefficients[MAX_STREAMS * MAX_STREAMS + 2 * MAX_STREAMS];
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    float* m = coefficients;
+    float* ow = coefficients + MAX_STREAMS * MAX_STREAMS;
+    float* iw = ow + MAX_STREAMS;
+    for (int i = threadIdx.x; i < streams * streams; i += blockDim.x) m[i] = mix ? mix[i] : 0.f;
+    for (int i = threadIdx.x; i < streams; i += blockDim.x) {
+        ow[i] = out_w ? out_w[i] : 0.f;
+        iw[i] = in_w ? in_w[i] : 1.f;
+    }
+    float4 weight[VEC_ITERS];
+    const int quads = hidden / 4;
+    if (normed) {                                           // (the norm's weights do not depend on the kernel ahead)
+#pragma unroll
+        for (int it = 0; it < VEC_ITERS; ++it) {
+            const int i = threadIdx.x + it * blockDim.x;
+            if (i < quads) weight[it] = reinterpret_cast<const float4*>(norm_w)[i];
+        }
+    }
+    __syncthreads();
+    pdl_wait();
+    const int r = blockIdx.x;
+    if (r >= rows) return;
+    const int source = rows_index ? rows_index[r] : r;
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)(source < 0 ? 0 : source) * hidden * streams);
+    const float4* yr = y ? reinterpret_cast<const float4*>(y + (size_t)r * hidden) : nullptr;
+    float4* ur = u ? reinterpret_cast<float4*>(u + (size_t)r * hidden) : nullptr;
+    float4 keep[VEC_ITERS];
+    float sum = 0.f;
+#pragma unroll
+    for (int it = 0; it < VEC_ITERS; ++it) {
+        const int i = threadIdx.x + it * blockDim.x;
+        if (i >= quads) break;
+        float4 xs[MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < MAX_STREAMS; ++s)
+            xs[s] = (s < streams && source >= 0) ? xr[(size_t)s * quads + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (yr) {
+            const float4 yi = yr[i];
+            float4 next[MAX_STREAMS];
+#pragma unroll
+            for (int t = 0; t < MAX_STREAMS; ++t) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int s = 0; s < MAX_STREAMS; ++s)
+                    if (s < streams && t < streams) acc = fma4(m[s * streams + t], xs[s], acc);
+                next[t] = fma4(ow[t < streams ? t : 0], yi, acc);
+            }
+#pragma unroll
+            for (int t = 0; t < MAX_STREAMS; ++t)
+                if (t < streams) {
+                    xs[t] = next[t];
+                    xr[(size_t)t * quads + i] = next[t];
+                }
+        }
+        if (ur) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int s = 0; s < MAX_STREAMS; ++s)
+                if (s < streams) acc = fma4(iw[s], xs[s], acc);
+            ur[i] = acc;
+            keep[it] = acc;
+            sum = fmaf(acc.x, acc.x, fmaf(acc.y, acc.y, fmaf(acc.z, acc.z, fmaf(acc.w, acc.w, sum))));
+        }
+    }
+    if (!normed) return;
+    sum = block_sum(sum, scratch);
+    const float inv = 1.0f / sqrtf(sum / (float)hidden + eps);
+    TO* nr = normed + (size_t)r * hidden;
+#pragma unroll
+    for (int it = 0; it < VEC_ITERS; ++it) {
+        const int i = threadIdx.x + it * blockDim.x;
+        if (i >= quads) break;
+        const float4 v = keep[it], w = weight[it];
+        store4(nr + 4 * (size_t)i, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
+    }
+}
+
 __global__ void softcap_rows_kernel(float* __restrict__ z, long long ld, int rows, int width, float cap) {
     pdl_launch_dependents();
     pdl_wait();
@@ -165,6 +266,20 @@ LIA_EXPORT int lia_hyper_step(float* x, const float* y, const float* mix, const 
     if (hidden <= 0 || streams <= 0 || streams > MAX_STREAMS || (y && (!mix || !out_w || rows_index)) ||
         (normed && (!u || !norm_w)) || (!y && !u))
         return LIA_ERR_SIZE;
+    const auto aligned = [](const void* p) { return ((uintptr_t)p & 15u) == 0; };
+    if (hidden % 4 == 0 && hidden <= 4 * VEC_ITERS * 512 && aligned(x) && aligned(y) && aligned(u) && aligned(norm_w) &&
+        (normed_dtype == LIA_F32 ? aligned(normed) : ((uintptr_t)normed & 7u) == 0)) {
+        // four elements a thread and step: as many threads as a row has groups of four, 64 to 512
+        const int quads = hidden / 4;
+        const int vec_threads = quads >= 512 ? 512 : quads <= 64 ? 64 : (quads + 31) / 32 * 32;
+        if (!normed || normed_dtype == LIA_F32)
+            return lia_launch(hyper_step_vec_kernel<float>, dim3(rows), dim3(vec_threads), 0, stream, x, y, mix, out_w, in_w,
+                              rows_index, u, norm_w, (float*)normed, rows, hidden, streams, eps);
+        if (normed_dtype == LIA_BF16)
+            return lia_launch(hyper_step_vec_kernel<__nv_bfloat16>, dim3(rows), dim3(vec_threads), 0, stream, x, y, mix, out_w,
+                              in_w, rows_index, u, norm_w, (__nv_bfloat16*)normed, rows, hidden, streams, eps);
+        return LIA_ERR_DTYPE;
+    }
     const int threads = hidden >= 2048 ? 512 : hidden >= 512 ? 256 : 128;
     if (!normed || normed_dtype == LIA_F32)
         return lia_launch(hyper_step_kernel<float>, dim3(rows), dim3(threads), 0, stream, x, y, mix, out_w, in_w,

@@ -115,6 +115,34 @@ retention_single_kernel(const float* __restrict__ rows, long long ld, const floa
     }
 }
 
+__device__ __forceinline__ float4 scaled(float4 v, float w) { return make_float4(v.x * w, v.y * w, v.z * w, v.w * w); }
+
+// [CHUNK][width] of a chunk's rows into shared memory (row stride `stride`, zero behind `len` rows), each row times
+// weight^(len - 1 - t) when weight_log2 is given; four elements at a time (`vec`: width and ld multiples of four, the
+// base 16-byte aligned), several loads in flight.
+__device__ __forceinline__ void load_chunk(float* __restrict__ dst, int stride, const float* __restrict__ src, long long ld,
+                                           int len, int width, bool vec, bool weighted, float weight_log2) {
+    if (vec) {
+        const int w4 = width / 4;
+#pragma unroll 4
+        for (int e = threadIdx.x; e < CHUNK * w4; e += blockDim.x) {
+            const int t = e / w4, i4 = e - t * w4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < len) v = *reinterpret_cast<const float4*>(src + (size_t)t * ld + 4 * i4);
+            if (weighted) v = scaled(v, exp2f((float)(len - 1 - t) * weight_log2));
+            *reinterpret_cast<float4*>(dst + t * stride + 4 * i4) = v;
+        }
+        return;
+    }
+    const int padded = (width + 3) & ~3;
+    for (int e = threadIdx.x; e < CHUNK * padded; e += blockDim.x) {
+        const int t = e / padded, i = e - t * padded;
+        float value = 0.f;
+        if (t < len && i < width) value = src[(size_t)t * ld + i] * (weighted ? exp2f((float)(len - 1 - t) * weight_log2) : 1.0f);
+        dst[t * stride + i] = value;
+    }
+}
+
 // which portion and which of its chunks the CTA `index` serves: false when there is none
 __device__ __forceinline__ bool find_chunk(const int* __restrict__ segments, int n_segments, int index, int* first_row,
                                            int* length, int* segment, int* chunk) {
@@ -136,7 +164,8 @@ __device__ __forceinline__ bool find_chunk(const int* __restrict__ segments, int
 // U [chunk, head, d, dv] = sum_j decay^(len-1-j) k_j v_j^T
 __global__ void __launch_bounds__(RET_THREADS)
 retention_sums_kernel(const float* __restrict__ rows, long long ld, const float* __restrict__ decay,
-                      const int* __restrict__ segments, int n_segments, float* __restrict__ sums, int heads, int d, int dv) {
+                      const int* __restrict__ segments, int n_segments, float* __restrict__ sums, int heads, int d, int dv,
+                      int vec) {
     extern __shared__ float sums_shared[];                // k [CHUNK][dp] weighted, v [CHUNK][dvp]
     pdl_launch_dependents();
     pdl_wait();
@@ -147,16 +176,9 @@ retention_sums_kernel(const float* __restrict__ rows, long long ld, const float*
     float* ks = sums_shared;
     float* vs = ks + CHUNK * dp;
     const float log_a = log2f(decay[h]);
-    for (int e = threadIdx.x; e < CHUNK * dp; e += blockDim.x) {
-        const int t = e / dp, i = e - t * dp;
-        float value = 0.f;
-        if (t < len && i < d) value = rows[(size_t)(first + t) * ld + (size_t)(heads + h) * d + i] * exp2f((float)(len - 1 - t) * log_a);
-        ks[e] = value;
-    }
-    for (int e = threadIdx.x; e < CHUNK * dvp; e += blockDim.x) {
-        const int t = e / dvp, j = e - t * dvp;
-        vs[e] = (t < len && j < dv) ? rows[(size_t)(first + t) * ld + (size_t)2 * heads * d + (size_t)h * dv + j] : 0.f;
-    }
+    const float* chunk_rows = rows + (size_t)first * ld;
+    load_chunk(ks, dp, chunk_rows + (size_t)(heads + h) * d, ld, len, d, vec, true, log_a);
+    load_chunk(vs, dvp, chunk_rows + (size_t)2 * heads * d + (size_t)h * dv, ld, len, dv, vec, false, 0.f);
     __syncthreads();
     float* U = sums + ((size_t)blockIdx.x * heads + h) * d * dv;
     const int tiles_j = dvp / 4, tiles = (dp / 4) * tiles_j;
@@ -171,6 +193,12 @@ retention_sums_kernel(const float* __restrict__ rows, long long ld, const float*
             for (int x = 0; x < 4; ++x)
 #pragma unroll
                 for (int y = 0; y < 4; ++y) acc[x][y] = fmaf(av[x], bv[y], acc[x][y]);
+        }
+        if (vec) {                                          // (d and dv multiples of four: whole rows of four)
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+                *reinterpret_cast<float4*>(U + (size_t)(i0 + x) * dv + j0) = make_float4(acc[x][0], acc[x][1], acc[x][2], acc[x][3]);
+            continue;
         }
 #pragma unroll
         for (int x = 0; x < 4; ++x)
@@ -200,13 +228,22 @@ retention_carry_kernel(const float* __restrict__ decay, const int* __restrict__ 
     const float last = exp2f((float)(count - (chunks - 1) * CHUNK) * log_a);
     const int size = d * dv;
     float* S = state + (size_t)slot * state_stride + (size_t)h * size;
+    // (a thread walks its element's chunks eight at a time: the eight loads are in flight together)
+    constexpr int AHEAD = 8;
+    const size_t chunk_stride = (size_t)heads * size;
     for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < size; e += gridDim.z * blockDim.x) {
         float value = S[e];
-        for (int c = 0; c < chunks; ++c) {
-            float* U = sums + ((size_t)(before + c) * heads + h) * size;
-            const float u = U[e];
-            U[e] = value;
-            value = fmaf(c + 1 < chunks ? full : last, value, u);
+        float* U = sums + ((size_t)before * heads + h) * size + e;
+        for (int c0 = 0; c0 < chunks; c0 += AHEAD) {
+            float u[AHEAD];
+#pragma unroll
+            for (int k = 0; k < AHEAD; ++k) u[k] = c0 + k < chunks ? U[(size_t)(c0 + k) * chunk_stride] : 0.f;
+#pragma unroll
+            for (int k = 0; k < AHEAD; ++k)
+                if (c0 + k < chunks) {
+                    U[(size_t)(c0 + k) * chunk_stride] = value;
+                    value = fmaf(c0 + k + 1 < chunks ? full : last, value, u[k]);
+                }
         }
         S[e] = value;
     }
@@ -216,7 +253,7 @@ template <typename TO>
 __global__ void __launch_bounds__(RET_THREADS)
 retention_output_kernel(const float* __restrict__ rows, long long ld, const float* __restrict__ decay,
                         const int* __restrict__ segments, int n_segments, const float* __restrict__ sums,
-                        TO* __restrict__ out, int heads, int d, int dv, float eps) {
+                        TO* __restrict__ out, int heads, int d, int dv, float eps, int vec) {
     extern __shared__ float out_shared[];  // qT [dp][CHUNK] (decayed), k [CHUNK][dp], v [CHUNK][dvp], A [CHUNK][CHUNK], o [CHUNK][dvp], powers [CHUNK + 1]
     pdl_launch_dependents();
     pdl_wait();
@@ -232,17 +269,27 @@ retention_output_kernel(const float* __restrict__ rows, long long ld, const floa
     float* powers = os + CHUNK * dvp;
     const float log_a = log2f(decay[h]);
     for (int i = threadIdx.x; i <= CHUNK; i += blockDim.x) powers[i] = exp2f((float)i * log_a);
-    for (int e = threadIdx.x; e < CHUNK * dp; e += blockDim.x) {
-        const int t = e / dp, i = e - t * dp;
-        const bool in = t < len && i < d;
-        const float* row = rows + (size_t)(first + t) * ld;
-        qT[i * CHUNK + t] = in ? row[(size_t)h * d + i] : 0.f;
-        ks[e] = in ? row[(size_t)(heads + h) * d + i] : 0.f;
+    const float* chunk_rows = rows + (size_t)first * ld;
+    if (vec) {
+        // the queries transposed: a lane a token (its stores fall into 32 banks), a warp four elements of the head
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll 4
+        for (int i0 = 4 * warp; i0 < d; i0 += 4 * (RET_THREADS / 32)) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (lane < len) v = *reinterpret_cast<const float4*>(chunk_rows + (size_t)lane * ld + (size_t)h * d + i0);
+            qT[(i0 + 0) * CHUNK + lane] = v.x;
+            qT[(i0 + 1) * CHUNK + lane] = v.y;
+            qT[(i0 + 2) * CHUNK + lane] = v.z;
+            qT[(i0 + 3) * CHUNK + lane] = v.w;
+        }
+    } else {
+        for (int e = threadIdx.x; e < CHUNK * dp; e += blockDim.x) {
+            const int t = e / dp, i = e - t * dp;
+            qT[i * CHUNK + t] = (t < len && i < d) ? chunk_rows[(size_t)t * ld + (size_t)h * d + i] : 0.f;
+        }
     }
-    for (int e = threadIdx.x; e < CHUNK * dvp; e += blockDim.x) {
-        const int t = e / dvp, j = e - t * dvp;
-        vs[e] = (t < len && j < dv) ? rows[(size_t)(first + t) * ld + (size_t)2 * heads * d + (size_t)h * dv + j] : 0.f;
-    }
+    load_chunk(ks, dp, chunk_rows + (size_t)(heads + h) * d, ld, len, d, vec, false, 0.f);
+    load_chunk(vs, dvp, chunk_rows + (size_t)2 * heads * d + (size_t)h * dv, ld, len, dv, vec, false, 0.f);
     __syncthreads();
     // A[t][j] = decay^(t-j) q_t . k_j for j <= t
     for (int e = threadIdx.x; e < CHUNK * CHUNK; e += blockDim.x) {
@@ -259,24 +306,64 @@ retention_output_kernel(const float* __restrict__ rows, long long ld, const floa
     const float* S = sums + ((size_t)blockIdx.x * heads + h) * d * dv;
     const int tiles_j = dvp / 4, tiles = (CHUNK / 4) * tiles_j;
     const bool aligned = (dv & 3) == 0;
-    for (int tile = threadIdx.x; tile < tiles; tile += blockDim.x) {
-        const int t0 = (tile / tiles_j) * 4, j0 = (tile % tiles_j) * 4;
+    // When every thread has at most one tile, the incoming state goes through shared memory CHUNK rows at a time (in the
+    // room of `os`, which is written only afterwards): every warp reads all of it, and the SM's L1 does not hold it.
+    const bool staged = tiles <= (int)blockDim.x;
+    for (int tile = threadIdx.x; tile < (staged ? (int)blockDim.x : tiles); tile += blockDim.x) {
+        const bool active = tile < tiles;
+        const int t0 = active ? (tile / tiles_j) * 4 : 0, j0 = active ? (tile % tiles_j) * 4 : 0;
         float acc[4][4] = {};
-        for (int i = 0; i < d; ++i) {
-            const float4 a = *reinterpret_cast<const float4*>(qT + i * CHUNK + t0);
-            float bv[4];
-            if (aligned) {
-                const float4 b = __ldg(reinterpret_cast<const float4*>(S + (size_t)i * dv + j0));
-                bv[0] = b.x, bv[1] = b.y, bv[2] = b.z, bv[3] = b.w;
-            } else {
+        if (staged) {
+            for (int i0 = 0; i0 < d; i0 += CHUNK) {
+                const int rows_now = min(CHUNK, d - i0);
+                if (aligned) {
+                    const int w4 = dv / 4;
+#pragma unroll 4
+                    for (int e = threadIdx.x; e < rows_now * w4; e += blockDim.x) {
+                        const int r = e / w4, c4 = e - r * w4;
+                        *reinterpret_cast<float4*>(os + r * dvp + 4 * c4) =
+                            __ldg(reinterpret_cast<const float4*>(S + (size_t)(i0 + r) * dv + 4 * c4));
+                    }
+                } else {
+                    for (int e = threadIdx.x; e < rows_now * dvp; e += blockDim.x) {
+                        const int r = e / dvp, c = e - r * dvp;
+                        os[e] = c < dv ? S[(size_t)(i0 + r) * dv + c] : 0.f;
+                    }
+                }
+                __syncthreads();
+                if (active) {
+#pragma unroll 8
+                    for (int ii = 0; ii < rows_now; ++ii) {
+                        const float4 a = *reinterpret_cast<const float4*>(qT + (i0 + ii) * CHUNK + t0);
+                        const float4 b = *reinterpret_cast<const float4*>(os + ii * dvp + j0);
+                        const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-                for (int y = 0; y < 4; ++y) bv[y] = j0 + y < dv ? S[(size_t)i * dv + j0 + y] : 0.f;
+                        for (int x = 0; x < 4; ++x)
+#pragma unroll
+                            for (int y = 0; y < 4; ++y) acc[x][y] = fmaf(av[x], bv[y], acc[x][y]);
+                    }
+                }
+                __syncthreads();
             }
-            const float av[4] = {a.x, a.y, a.z, a.w};
+            if (!active) continue;
+        } else {
+#pragma unroll 8
+            for (int i = 0; i < d; ++i) {
+                const float4 a = *reinterpret_cast<const float4*>(qT + i * CHUNK + t0);
+                float bv[4];
+                if (aligned) {
+                    const float4 b = __ldg(reinterpret_cast<const float4*>(S + (size_t)i * dv + j0));
+                    bv[0] = b.x, bv[1] = b.y, bv[2] = b.z, bv[3] = b.w;
+                } else {
 #pragma unroll
-            for (int x = 0; x < 4; ++x)
+                    for (int y = 0; y < 4; ++y) bv[y] = j0 + y < dv ? S[(size_t)i * dv + j0 + y] : 0.f;
+                }
+                const float av[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
-                for (int y = 0; y < 4; ++y) acc[x][y] = fmaf(av[x], bv[y], acc[x][y]);
+                for (int x = 0; x < 4; ++x)
+#pragma unroll
+                    for (int y = 0; y < 4; ++y) acc[x][y] = fmaf(av[x], bv[y], acc[x][y]);
+            }
         }
 #pragma unroll
         for (int x = 0; x < 4; ++x)
@@ -358,6 +445,7 @@ LIA_EXPORT int lia_retention(const float* rows, long long ld, const float* decay
         if (max_chunks <= 0 || !scratch || scratch_floats < lia_retention_scratch_floats(max_chunks, heads, d, dv))
             return LIA_ERR_SIZE;
         const int dp = (d + 3) & ~3, dvp = (dv + 3) & ~3;
+        const int vec = ((d | dv) & 3) == 0 && (ld & 3) == 0 && (((uintptr_t)rows | (uintptr_t)scratch) & 15u) == 0 ? 1 : 0;
         const size_t sums_bytes = (size_t)CHUNK * (dp + dvp) * sizeof(float);
         const size_t out_bytes = output_shared_bytes(d, dv);
         static bool raised = false;
@@ -368,19 +456,19 @@ LIA_EXPORT int lia_retention(const float* rows, long long ld, const float* decay
             raised = true;
         }
         code = lia_launch(retention_sums_kernel, dim3(max_chunks, heads), dim3(RET_THREADS), sums_bytes, stream, rows, ld,
-                          decay, segments, n_segments, scratch, heads, d, dv);
+                          decay, segments, n_segments, scratch, heads, d, dv, vec);
         if (code != LIA_OK) return code;
-        const int parts = (d * dv + RET_THREADS * 4 - 1) / (RET_THREADS * 4);
+        const int parts = (d * dv + RET_THREADS - 1) / RET_THREADS;          // one element a thread
         code = lia_launch(retention_carry_kernel, dim3(n_segments, heads, parts), dim3(RET_THREADS), 0, stream, decay,
                           segments, n_segments, slots, scratch, state, state_stride, heads, d, dv);
         if (code != LIA_OK) return code;
         if (out_dtype == LIA_F32)
             code = lia_launch(retention_output_kernel<float>, dim3(max_chunks, heads), dim3(RET_THREADS), out_bytes, stream,
-                              rows, ld, decay, segments, n_segments, (const float*)scratch, (float*)out, heads, d, dv, eps);
+                              rows, ld, decay, segments, n_segments, (const float*)scratch, (float*)out, heads, d, dv, eps, vec);
         else
             code = lia_launch(retention_output_kernel<__nv_bfloat16>, dim3(max_chunks, heads), dim3(RET_THREADS), out_bytes,
                               stream, rows, ld, decay, segments, n_segments, (const float*)scratch, (__nv_bfloat16*)out,
-                              heads, d, dv, eps);
+                              heads, d, dv, eps, vec);
         if (code != LIA_OK) return code;
     }
     if (n_single > 0) {

@@ -376,7 +376,7 @@ def test_router_scores_choice_ties_and_weights():
     n, hidden, experts, top, scale = 23, 48, 7, 3, 1.9
     g = torch.Generator().manual_seed(3)
     x = torch.randn(n, hidden, generator=g)
-    router = torch.randn(experts + 1, hidden, generator=g)
+    router = torch.randn(experts + 1, hidden, generator=g) * 0.2
     router[4] = router[1]                                                   # two experts of equal score: the lower index first
     ids = torch.zeros(n, top, dtype=torch.int32, device="cuda")
     weights, gate = torch.zeros(n, top, device="cuda"), torch.zeros(n, device="cuda")
