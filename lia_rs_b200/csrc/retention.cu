@@ -90,10 +90,24 @@ retention_single_kernel(const float* __restrict__ rows, long long ld, const floa
     for (int j = lane; j < dv; j += lanes) {
         const float vj = v[j];
         float acc = 0.f;
-        for (int i = group; i < d; i += groups) {
-            const float s = fmaf(a, S[(size_t)i * dv + j], ks[i] * vj);
-            S[(size_t)i * dv + j] = s;
-            acc = fmaf(s, qs[i], acc);
+        // (eight rows of the state at a time: their loads are in flight together; the sums keep their order)
+        constexpr int AHEAD = 8;
+        for (int i0 = group; i0 < d; i0 += groups * AHEAD) {
+            float held[AHEAD];
+#pragma unroll
+            for (int k = 0; k < AHEAD; ++k) {
+                const int i = i0 + k * groups;
+                held[k] = i < d ? S[(size_t)i * dv + j] : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < AHEAD; ++k) {
+                const int i = i0 + k * groups;
+                if (i < d) {
+                    const float s = fmaf(a, held[k], ks[i] * vj);
+                    S[(size_t)i * dv + j] = s;
+                    acc = fmaf(s, qs[i], acc);
+                }
+            }
         }
         if (groups > 1) partial[group * lanes + lane] = acc;       // (groups > 1 only when dv <= lanes: one j a lane)
         else partial[j] = acc;
