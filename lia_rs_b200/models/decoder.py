@@ -209,6 +209,9 @@ class DecoderModel:
         last = len(spec.schedule) - 1
         for position, entry in enumerate(spec.schedule):
             junction = self.junctions.get(position)
+            owed = getattr(ctx, "owed", None)
+            if owed is not None and (junction is not None or type(self.layers[entry.layer]) is not type(owed[0])):
+                owed[0].settle(ctx, h)
             if junction is not None:
                 junction.forward(ctx, h, first)
             kv = ctx.kv_view(entry.cache, entry.writes) if entry.cache is not None else None
@@ -218,6 +221,11 @@ class DecoderModel:
                 picked = layer.forward(ctx, h, kv=kv, state=ctx.state(position), rows=ctx.out_rows, n_rows=ctx.n_out, **more)
             else:
                 layer.forward(ctx, h, kv=kv, state=ctx.state(position), **more)
+        owed = getattr(ctx, "owed", None)
+        if owed is not None:
+            if ctx.n_out > 0:
+                owed[0].settle(ctx, h)          # (without wanted rows nobody reads the stream again)
+            ctx.owed = None
         if ctx.n_out == 0:
             return ctx.logits_buffer(0, spec.vocab_size)
         y = ctx.buffer("model.y", (ctx.n_out, spec.hidden_size), rt.compute_dtype)

@@ -222,6 +222,13 @@ class Arrangement:
         is always right."""
         return tuple(count for _, _, count, _ in ctx.segments)
 
+    def settle(self, ctx, residual) -> None:
+        """A layer may leave its last write to the residual stream to the layer behind it, which then does it together
+        with its own first read (it says so in `ctx.owed`, whose first element is the layer).  The model calls `settle`
+        where no such layer follows: ahead of a layer of another class, of a junction, and of the final norm.  The
+        default owes nothing."""
+        return None
+
     @staticmethod
     def tensor_specs(layer_spec, prefix: str) -> list:
         raise NotImplementedError

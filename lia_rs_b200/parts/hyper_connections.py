@@ -7,7 +7,8 @@ and out_q [s]:
     u = sum_s in_q[s] x_s;   y = sublayer_q(norm_q(u));   x_t <- sum_s mix_q[s, t] x_s + out_q[t] y   (all t from the old x)
 
 One kernel (csrc/hyper_connections.cu) does a sublayer's write-back together with the read and the norm of the next
-sublayer of the layer, in one pass over the token's row, so a layer costs three passes over the streams.  The sublayers
+sublayer, in one pass over the token's row; a layer's last write-back is left to the layer behind it (`ctx.owed`), which
+does it in the pass of its first read, so a layer costs two passes over the streams and the model one more (`settle`).  The sublayers
 store their output into a 32-bit buffer of the arrangement.  The norms must be RMS norms (`rms_record`).
 
 `options`: {"streams": s, "learned": bool (default True)}.  Without learned coefficients (in = out = 1, mix = the
@@ -116,14 +117,27 @@ class HyperConnectionBlock(Arrangement):
         y = ctx.buffer("block.sublayer", (n, hidden), torch.float32)
         x1 = ctx.buffer("block.x", (n, hidden), dtype)
         (in1, mix1, out1), (w1, eps1) = self.coefficients[0], self.norms[0]
-        ops.hyper_step(residual, s, in_weights=in1, u=u, norm_weight=w1, normed=x1, eps=eps1)
+        owed = getattr(ctx, "owed", None)
+        if owed is not None:
+            # the layer ahead left its last write-back: it is done in the pass of this layer's first read
+            ctx.owed = None
+            ops.hyper_step(residual, s, y=owed[1], mix=owed[2], out_weights=owed[3], in_weights=in1, u=u, norm_weight=w1,
+                           normed=x1, eps=eps1)
+        else:
+            ops.hyper_step(residual, s, in_weights=in1, u=u, norm_weight=w1, normed=x1, eps=eps1)
         self._sublayer(ctx, self.mixer, x1, y, kv=kv, state=state)
         if self.feed_forward is None:
-            ops.hyper_step(residual, s, y=y, mix=mix1, out_weights=out1)
+            ctx.owed = (self, y, mix1, out1)
             return None
         (in2, mix2, out2), (w2, eps2) = self.coefficients[1], self.norms[1]
         x2 = ctx.buffer("block.x2", (n, hidden), dtype)
         ops.hyper_step(residual, s, y=y, mix=mix1, out_weights=out1, in_weights=in2, u=u, norm_weight=w2, normed=x2, eps=eps2)
         self._sublayer(ctx, self.feed_forward, x2, y)
-        ops.hyper_step(residual, s, y=y, mix=mix2, out_weights=out2)
+        ctx.owed = (self, y, mix2, out2)
         return None
+
+    def settle(self, ctx, residual) -> None:
+        owed = getattr(ctx, "owed", None)
+        if owed is not None and owed[0] is self:
+            ctx.owed = None
+            ops.hyper_step(residual, self.n_streams, y=owed[1], mix=owed[2], out_weights=owed[3])
