@@ -126,7 +126,8 @@ LIA_EXPORT int lia_attention_generic(const void* q, const void* k_pages, const v
 // leading part of the first key part (attention through a shared latent: k1 = v = the latent, k2 = the rotated part)
 // passes the k1 pages as values with v_stride = dk1.  q1, q2 and out are addressed by a token stride and a head stride,
 // so that heads may lie side by side in a token's row or in planes of their own.  `sink`: one is added to the softmax's
-// denominator (a key of score 0 that has no value).  Sizes: dk1 + dk2 up to 1,024, dv up to 512.
+// denominator (a key of score 0 that has no value).  `softcap` > 0: score <- softcap * tanh(score / softcap) ahead of
+// the softmax.  Sizes: dk1 + dk2 up to 1,024, dv up to 512.
 namespace {
 constexpr int GENERAL_MAX_DK = 1024;
 
@@ -138,7 +139,7 @@ attention_general_kernel(const T* __restrict__ q1, long long q1_ts, long long q1
                          const int* __restrict__ positions, const int* __restrict__ slots,
                          const int* __restrict__ block_table, int table_stride, const int* __restrict__ rows,
                          T* __restrict__ out, long long o_ts, long long o_hs, int n_tokens, int nq, int nkv,
-                         int page_size, int window, float scale, int sink, int num_pages, int* __restrict__ error_flag) {
+                         int page_size, int window, float scale, float softcap, int sink, int num_pages, int* __restrict__ error_flag) {
     extern __shared__ float q_general[];                    // [WARPS][dk1 + dk2]
     pdl_launch_dependents();
     pdl_wait();
@@ -187,6 +188,7 @@ attention_general_kernel(const T* __restrict__ q1, long long q1_ts, long long q1
                 for (int i = 0; i < dk2; ++i) dot = fmaf(qs[dk1 + i], to_float(k2row[i]), dot);
             }
             score = dot * scale;
+            if (softcap > 0.f) score = softcap * tanhf(score / softcap);
         }
         const float chunk_max = warp_max(score);
         const float new_max = fmaxf(running_max, chunk_max);
@@ -223,7 +225,7 @@ int launch_general(const void* q1, long long q1_ts, long long q1_hs, const void*
                    const void* k1_pages, int dk1, const void* k2_pages, int dk2, const void* v_pages, int v_stride, int dv,
                    const int* positions, const int* slots, const int* block_table, int table_stride, const int* rows,
                    void* out, long long o_ts, long long o_hs, int n_tokens, int nq, int nkv, int page_size, int window,
-                   float scale, int sink, int num_pages, int* error_flag, cudaStream_t stream) {
+                   float scale, float softcap, int sink, int num_pages, int* error_flag, cudaStream_t stream) {
     const long long blocks = ((long long)n_tokens * nq + WARPS - 1) / WARPS;
     if (blocks > 2147483647LL) return LIA_ERR_SIZE;
     const size_t smem = (size_t)WARPS * (dk1 + dk2) * sizeof(float);
@@ -232,7 +234,7 @@ int launch_general(const void* q1, long long q1_ts, long long q1_hs, const void*
     return lia_launch(attention_general_kernel<T, DVC>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, stream,       \
                       (const T*)q1, q1_ts, q1_hs, (const T*)q2, q2_ts, q2_hs, (const T*)k1_pages, dk1,                \
                       (const T*)k2_pages, dk2, (const T*)v_pages, v_stride, dv, positions, slots, block_table,        \
-                      table_stride, rows, (T*)out, o_ts, o_hs, n_tokens, nq, nkv, page_size, window, scale, sink,     \
+                      table_stride, rows, (T*)out, o_ts, o_hs, n_tokens, nq, nkv, page_size, window, scale, softcap, sink,     \
                       num_pages, error_flag)
     if (chunks <= 2) LIA_GENERAL(2);
     if (chunks <= 4) LIA_GENERAL(4);
@@ -247,7 +249,7 @@ LIA_EXPORT int lia_attention_general(const void* q1, long long q1_ts, long long 
                                      const void* v_pages, int v_stride, int dv, int dtype, const int* positions,
                                      const int* slots, const int* block_table, int table_stride, const int* rows,
                                      void* out, long long o_ts, long long o_hs, int n_tokens, int nq, int nkv,
-                                     int page_size, int window, float scale, int sink, int num_pages, int* error_flag,
+                                     int page_size, int window, float scale, float softcap, int sink, int num_pages, int* error_flag,
                                      cudaStream_t stream) {
     if (n_tokens <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || dk1 <= 0 || dk2 < 0 || dk1 + dk2 > GENERAL_MAX_DK || dv <= 0 || dv > 512 ||
@@ -256,11 +258,11 @@ LIA_EXPORT int lia_attention_general(const void* q1, long long q1_ts, long long 
     if (dtype == LIA_F32)
         return launch_general<float>(q1, q1_ts, q1_hs, q2, q2_ts, q2_hs, k1_pages, dk1, k2_pages, dk2, v_pages, v_stride,
                                      dv, positions, slots, block_table, table_stride, rows, out, o_ts, o_hs, n_tokens, nq,
-                                     nkv, page_size, window, scale, sink, num_pages, error_flag, stream);
+                                     nkv, page_size, window, scale, softcap, sink, num_pages, error_flag, stream);
     if (dtype == LIA_BF16)
         return launch_general<__nv_bfloat16>(q1, q1_ts, q1_hs, q2, q2_ts, q2_hs, k1_pages, dk1, k2_pages, dk2, v_pages,
                                              v_stride, dv, positions, slots, block_table, table_stride, rows, out, o_ts,
-                                             o_hs, n_tokens, nq, nkv, page_size, window, scale, sink, num_pages,
+                                             o_hs, n_tokens, nq, nkv, page_size, window, scale, softcap, sink, num_pages,
                                              error_flag, stream);
     return LIA_ERR_DTYPE;
 }

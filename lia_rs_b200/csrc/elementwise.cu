@@ -181,6 +181,65 @@ LIA_EXPORT int lia_rmsnorm(const float* x, const int* rows_index, const void* we
 }
 
 // ---------------------------------------------------------------------------------------
+// Layer norm: y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b, all sums 32-bit, the variance taken of
+// the deviations (second pass over the row, which the CTA keeps in shared memory).  out row r comes from row
+// rows_index[r] of x when an index is given (a negative index gives a row of zeros).
+template <typename TW, typename TO>
+__global__ void layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows_index,
+                                 const TW* __restrict__ weight, const TW* __restrict__ bias, TO* __restrict__ out,
+                                 int rows, int hidden, float eps) {
+    extern __shared__ float layernorm_row[];
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    if (r >= rows) return;
+    const int src = rows_index ? rows_index[r] : r;
+    TO* dst = out + (size_t)r * hidden;
+    if (src < 0) {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_float<TO>(0.f);
+        return;
+    }
+    const float* row = x + (size_t)src * hidden;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = row[i];
+        layernorm_row[i] = v;
+        sum += v;
+    }
+    const float mean = block_sum(sum, scratch) / (float)hidden;
+    float squares = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float c = layernorm_row[i] - mean;
+        squares = fmaf(c, c, squares);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(squares, scratch) / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        dst[i] = from_float<TO>(fmaf((layernorm_row[i] - mean) * inv, to_float(weight[i]), bias ? to_float(bias[i]) : 0.f));
+}
+
+// x [.., hidden] 32-bit; weight and bias [hidden] of one element type (bias may be null); out [rows, hidden].
+LIA_EXPORT int lia_layernorm(const float* x, const int* rows_index, const void* weight, const void* bias, int weight_dtype,
+                             void* out, int out_dtype, int rows, int hidden, float eps, cudaStream_t stream) {
+    if (rows <= 0) return LIA_OK;
+    if (hidden <= 0 || (size_t)hidden * sizeof(float) > 200 * 1024) return LIA_ERR_SIZE;
+    const dim3 block(hidden >= 2048 ? 512 : hidden >= 512 ? 256 : 128);
+    const size_t bytes = (size_t)hidden * sizeof(float);
+#define LIA_LAYERNORM(TW, TO)                                                                                       \
+    {                                                                                                               \
+        if (bytes > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<TW, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+        return lia_launch(layernorm_kernel<TW, TO>, dim3(rows), block, bytes, stream, x, rows_index, (const TW*)weight, \
+                          (const TW*)bias, (TO*)out, rows, hidden, eps);                                           \
+    }
+    if (weight_dtype == LIA_BF16 && out_dtype == LIA_BF16) LIA_LAYERNORM(__nv_bfloat16, __nv_bfloat16)
+    if (weight_dtype == LIA_BF16 && out_dtype == LIA_F32) LIA_LAYERNORM(__nv_bfloat16, float)
+    if (weight_dtype == LIA_F32 && out_dtype == LIA_BF16) LIA_LAYERNORM(float, __nv_bfloat16)
+    if (weight_dtype == LIA_F32 && out_dtype == LIA_F32) LIA_LAYERNORM(float, float)
+#undef LIA_LAYERNORM
+    return LIA_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------
 // Rotary encoding (rotate-half over the first `rotary_dim` elements of each head; 0 = none)
 // of q and k, fused with the append of k and v to the paged cache.
 //   qkv      [n_tokens, (nq + 2 nkv) d] 32-bit: q heads, then k heads, then v heads

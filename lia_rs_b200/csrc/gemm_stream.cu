@@ -118,7 +118,7 @@ struct Args {
     int stages, early, chunks, ck;   // ring; stages asked for before the tokens' rows; K chunks per block; elements of K per chunk (a multiple of 64)
     int blocks, x_pitch, stage_bytes, half_bytes;
     int norm, out_bf16;              // norm: 0 none, 1 weight bf16, 2 weight f32
-    int activation;                  // STORE only: 0 none, 1 GELU (tanh form), 2 SiLU, applied to alpha * sum before the store
+    int activation;                  // STORE only: 0 none, 1 GELU (tanh form), 2 SiLU, 3 ReLU squared, 4 ReLU, applied to alpha * sum before the store
     float alpha, eps;
     int* error_flag;
 };
@@ -376,6 +376,9 @@ gemm_stream_kernel(Args a) {
                             value = value / (1.0f + expf(-2.0f * u));
                         } else if (MODE == GEMM_STORE && a.activation == 2) {
                             value = value / (1.0f + expf(-value));
+                        } else if (MODE == GEMM_STORE && a.activation >= 3) {          // 3: relu(z)^2, 4: relu(z)
+                            value = fmaxf(value, 0.f);
+                            if (a.activation == 3) value *= value;
                         }
                         if (a.out_bf16) reinterpret_cast<__nv_bfloat16*>(a.out)[(size_t)token * a.ldo + f] = __float2bfloat16_rn(value);
                         else reinterpret_cast<float*>(a.out)[(size_t)token * a.ldo + f] = value;
@@ -722,13 +725,13 @@ LIA_EXPORT int lia_gemm_stream_stages(int mode, int M, int N, int K, int with_no
 // pointers that are not 16-byte aligned (bulk copies and 16-byte loads need both), and sizes whose rows do not
 // fit in shared memory beside a ring (ask lia_gemm_stream_stages first).  `stages_cap` > 0 limits the ring;
 // `early_stages` > 0 sets how many stages the producer asks for before the tokens' rows have been asked for (default 2).
-// `activation` (STORE only): 1 the tanh form of GELU, 2 SiLU, applied to the 32-bit result before it is stored.
+// `activation` (STORE only): 1 the tanh form of GELU, 2 SiLU, 3 the square of ReLU, 4 ReLU, applied to the 32-bit result before it is stored.
 LIA_EXPORT int lia_gemm_stream(int mode, const void* X, int ldx, const void* W, int ldw, void* out, int out_dtype,
                                int ldo, int M, int N, int K, float alpha, const float* norm_src, int ld_norm,
                                const void* norm_weight, int norm_weight_dtype, float eps, int sms, int stages_cap,
                                int early_stages, int activation, int* error_flag, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return LIA_OK;
-    if (activation < 0 || activation > 2 || (activation && mode != GEMM_STORE)) return LIA_ERR_SIZE;
+    if (activation < 0 || activation > 4 || (activation && mode != GEMM_STORE)) return LIA_ERR_SIZE;
     if (M > TOKENS || K <= 0 || K % 64 || ldw % 8 || ldw < K || ldo < N || sms <= 0) return LIA_ERR_SIZE;
     if ((uintptr_t)W & 15u) return LIA_ERR_ALIGN;
     if (norm_src) {

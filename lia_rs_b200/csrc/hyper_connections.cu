@@ -12,7 +12,8 @@
 //    Either half may be left out.  `rows_index` (only without y) gathers: output row r is computed from row
 //    rows_index[r] of x.
 //  * `softcap_rows`: z <- cap * tanh(z / cap), in place on 32-bit rows.
-//  * `gate_rows`: o <- o * f(g) element by element, f the logistic function or SiLU, g 32-bit rows of any stride.
+//  * `gate_rows`: o <- o * f(g), f the logistic function or SiLU, g 32-bit rows of any stride; one gate element for
+//    every `span` neighbouring elements of o (span 1: element by element; span = a head's size: one gate a head).
 //
 // Everything is 32-bit but the normed rows and the gated rows.  The order of a row's additions depends on the width
 // and the number of streams alone.
@@ -220,14 +221,14 @@ __global__ void softcap_rows_kernel(float* __restrict__ z, long long ld, int row
 
 template <typename T, int ACT>
 __global__ void gate_rows_kernel(T* __restrict__ o, long long ld_o, const float* __restrict__ g, long long ld_g, int rows,
-                                 int width) {
+                                 int width, int span) {
     pdl_launch_dependents();
     pdl_wait();
     const long long total = (long long)rows * width;
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
         const long long r = e / width;
         const int i = (int)(e - r * width);
-        const float z = g[r * ld_g + i];
+        const float z = g[r * ld_g + i / span];
         const float s = 1.0f / (1.0f + expf(-z));
         const float f = ACT == 2 ? z * s : s;
         o[r * ld_o + i] = from_float<T>(to_float(o[r * ld_o + i]) * f);
@@ -298,15 +299,15 @@ LIA_EXPORT int lia_softcap_rows(float* z, long long ld, int rows, int width, flo
                       width, cap);
 }
 
-// o [rows, width] of `dtype` with row stride ld_o, in place: o <- o * f(g), g 32-bit with row stride ld_g; act 1: the
-// logistic function, 2: SiLU.
+// o [rows, width] of `dtype` with row stride ld_o, in place: o[r, i] <- o[r, i] * f(g[r, i / span]), g 32-bit with row
+// stride ld_g; act 1: the logistic function, 2: SiLU.
 LIA_EXPORT int lia_gate_rows(void* o, int dtype, long long ld_o, const float* g, long long ld_g, int rows, int width,
-                             int act, cudaStream_t stream) {
+                             int act, int span, cudaStream_t stream) {
     if (rows <= 0 || width <= 0) return LIA_OK;
-    if (ld_o < width || ld_g < width || act < 1 || act > 2) return LIA_ERR_SIZE;
+    if (span <= 0 || ld_o < width || ld_g < (width + span - 1) / span || act < 1 || act > 2) return LIA_ERR_SIZE;
     const int blocks = grid_for((long long)rows * width);
 #define LIA_GATE(T, ACT)                                                                                             \
-    return lia_launch(gate_rows_kernel<T, ACT>, dim3(blocks), dim3(256), 0, stream, (T*)o, ld_o, g, ld_g, rows, width)
+    return lia_launch(gate_rows_kernel<T, ACT>, dim3(blocks), dim3(256), 0, stream, (T*)o, ld_o, g, ld_g, rows, width, span)
     if (dtype == LIA_F32) {
         if (act == 1) LIA_GATE(float, 1);
         LIA_GATE(float, 2);

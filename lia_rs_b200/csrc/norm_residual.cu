@@ -48,10 +48,12 @@ __device__ __forceinline__ float gelu_tanh(float z) {
     return z / (1.0f + expf(-2.0f * u));
 }
 
-template <int ACT>
-__device__ __forceinline__ float activate(float z) {
-    if (ACT == 1) return gelu_tanh(z);
-    if (ACT == 2) return z / (1.0f + expf(-z));
+// act: 0 identity, 1 GELU (tanh form), 2 SiLU, 3 the square of ReLU, 4 ReLU
+__device__ __forceinline__ float activate(int act, float z) {
+    if (act == 1) return gelu_tanh(z);
+    if (act == 2) return z / (1.0f + expf(-z));
+    if (act == 3) { const float r = fmaxf(z, 0.f); return r * r; }
+    if (act == 4) return fmaxf(z, 0.f);
     return z;
 }
 
@@ -67,10 +69,11 @@ template <> __device__ __forceinline__ void store_four<__nv_bfloat16>(__nv_bfloa
     *reinterpret_cast<uint2*>(dst) = v;
 }
 
-// four elements a thread: rows whose width and strides are multiples of 4 from 16-byte aligned bases
-template <typename TO, int ACT>
+// four elements a thread: rows whose width and strides are multiples of 4 from 16-byte aligned bases.  `gated`: the
+// row holds `width` gate elements and then `width` more, out = act(gate) * the other.
+template <typename TO>
 __global__ void activation_rows4_kernel(const float* __restrict__ in, long long ld_in, TO* __restrict__ out,
-                                        long long ld_out, int rows, int quads) {
+                                        long long ld_out, int rows, int quads, int act, int gated) {
     pdl_launch_dependents();
     pdl_wait();
     const long long total = (long long)rows * quads;
@@ -78,20 +81,24 @@ __global__ void activation_rows4_kernel(const float* __restrict__ in, long long 
         const long long r = e / quads;
         const int i = (int)(e - r * quads) * 4;
         const float4 z = *reinterpret_cast<const float4*>(in + r * ld_in + i);
-        store_four<TO>(out + r * ld_out + i, activate<ACT>(z.x), activate<ACT>(z.y), activate<ACT>(z.z), activate<ACT>(z.w));
+        float4 u = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (gated) u = *reinterpret_cast<const float4*>(in + r * ld_in + 4 * quads + i);
+        store_four<TO>(out + r * ld_out + i, activate(act, z.x) * u.x, activate(act, z.y) * u.y, activate(act, z.z) * u.z,
+                       activate(act, z.w) * u.w);
     }
 }
 
-template <typename TO, int ACT>
+template <typename TO>
 __global__ void activation_rows_kernel(const float* __restrict__ in, long long ld_in, TO* __restrict__ out,
-                                       long long ld_out, int rows, int width) {
+                                       long long ld_out, int rows, int width, int act, int gated) {
     pdl_launch_dependents();
     pdl_wait();
     const long long total = (long long)rows * width;
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
         const long long r = e / width;
         const int i = (int)(e - r * width);
-        out[r * ld_out + i] = from_float<TO>(activate<ACT>(in[r * ld_in + i]));
+        const float u = gated ? in[r * ld_in + width + i] : 1.f;
+        out[r * ld_out + i] = from_float<TO>(activate(act, in[r * ld_in + i]) * u);
     }
 }
 }  // namespace
@@ -113,32 +120,25 @@ LIA_EXPORT int lia_norm_residual(const float* y, const float* bias, const float*
     return LIA_ERR_DTYPE;
 }
 
-// out[r, i] = act(in[r, i]), i < width; act: 0 identity, 1 GELU (tanh form), 2 SiLU.  Row strides in elements.
+// out[r, i] = act(in[r, i]), i < width, or with `gated` act(in[r, i]) * in[r, width + i]; act: 0 identity, 1 GELU
+// (tanh form), 2 SiLU, 3 the square of ReLU, 4 ReLU.  Row strides in elements.
 LIA_EXPORT int lia_activation_rows(const float* in, long long ld_in, void* out, int out_dtype, long long ld_out,
-                                   int rows, int width, int act, cudaStream_t stream) {
+                                   int rows, int width, int act, int gated, cudaStream_t stream) {
     if (rows <= 0 || width <= 0) return LIA_OK;
-    if (ld_in < width || ld_out < width || act < 0 || act > 2) return LIA_ERR_SIZE;
+    if (ld_in < (gated ? 2 : 1) * (long long)width || ld_out < width || act < 0 || act > 4) return LIA_ERR_SIZE;
     const bool four = width % 4 == 0 && ld_in % 4 == 0 && ld_out % 4 == 0 && ((uintptr_t)in & 15u) == 0 && ((uintptr_t)out & 15u) == 0;
     const long long total = four ? (long long)rows * (width / 4) : (long long)rows * width;
     const int blocks = (int)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
-#define LIA_ACT(TO, ACT)                                                                                                 \
+#define LIA_ACT(TO)                                                                                                      \
     {                                                                                                                    \
         if (four)                                                                                                        \
-            return lia_launch(activation_rows4_kernel<TO, ACT>, dim3(blocks), dim3(256), 0, stream, in, ld_in, (TO*)out, \
-                              ld_out, rows, width / 4);                                                                  \
-        return lia_launch(activation_rows_kernel<TO, ACT>, dim3(blocks), dim3(256), 0, stream, in, ld_in, (TO*)out,     \
-                          ld_out, rows, width);                                                                          \
+            return lia_launch(activation_rows4_kernel<TO>, dim3(blocks), dim3(256), 0, stream, in, ld_in, (TO*)out,     \
+                              ld_out, rows, width / 4, act, gated);                                                      \
+        return lia_launch(activation_rows_kernel<TO>, dim3(blocks), dim3(256), 0, stream, in, ld_in, (TO*)out,          \
+                          ld_out, rows, width, act, gated);                                                              \
     }
-    if (out_dtype == LIA_F32) {
-        if (act == 0) LIA_ACT(float, 0)
-        if (act == 1) LIA_ACT(float, 1)
-        LIA_ACT(float, 2)
-    }
-    if (out_dtype == LIA_BF16) {
-        if (act == 0) LIA_ACT(__nv_bfloat16, 0)
-        if (act == 1) LIA_ACT(__nv_bfloat16, 1)
-        LIA_ACT(__nv_bfloat16, 2)
-    }
+    if (out_dtype == LIA_F32) LIA_ACT(float)
+    if (out_dtype == LIA_BF16) LIA_ACT(__nv_bfloat16)
 #undef LIA_ACT
     return LIA_ERR_DTYPE;
 }

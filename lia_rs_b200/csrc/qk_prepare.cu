@@ -64,8 +64,9 @@ qkv_prepare_kernel(const float* __restrict__ rows, long long ld, const float* __
                    float* __restrict__ v_first, const int* __restrict__ positions, const int* __restrict__ slots,
                    const int* __restrict__ block_table, int table_stride, T* __restrict__ q_out,
                    T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens, int nq, int nkv, int d, int dv,
-                   int page_size, int num_pages, int write_kv, int* __restrict__ error_flag) {
+                   int page_size, int num_pages, int write_kv, int norm_whole, int* __restrict__ error_flag) {
     extern __shared__ float prep_shared[];                 // [rot_dims] cosines then sines, then [PREP_WARPS][d]
+    __shared__ float whole_scratch[32];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -82,11 +83,29 @@ qkv_prepare_kernel(const float* __restrict__ rows, long long ld, const float* __
     const long long cache_row = write_kv ? page_row(block_table, table_stride, slot, pos, page_size, num_pages, error_flag) : -1;
     const float* row = rows + (size_t)t * ld;
     float* h = heads + (size_t)warp * d;
+    // norm_whole: one root mean square over all of q's elements (bias added) and one over all of k's, weights of those sizes
+    float whole_inv[2] = {1.f, 1.f};
+    if (norm_whole) {
+        for (int part = 0; part < 2; ++part) {
+            const int first = part ? nq * d : 0, width = part ? nkv * d : nq * d;
+            float sum = 0.f;
+            for (int i = threadIdx.x; i < width; i += blockDim.x) {
+                const float v = row[first + i] + (bias ? bias[first + i] : 0.f);
+                sum = fmaf(v, v, sum);
+            }
+            sum = block_sum(sum, whole_scratch);
+            whole_inv[part] = 1.0f / sqrtf(sum / (float)width + eps);
+        }
+    }
     for (int head = warp; head < nq + nkv; head += PREP_WARPS) {
         const bool is_q = head < nq;
         for (int i = lane; i < d; i += 32) h[i] = row[head * d + i] + (bias ? bias[head * d + i] : 0.f);
+        if (norm_whole) {
+            const float* w = is_q ? q_norm + (size_t)head * d : k_norm + (size_t)(head - nq) * d;
+            for (int i = lane; i < d; i += 32) h[i] = h[i] * whole_inv[is_q ? 0 : 1] * w[i];
+        }
         __syncwarp();
-        norm_and_rotate(h, d, is_q ? q_norm : k_norm, eps, 0, rot_dims, rotation, lane);
+        norm_and_rotate(h, d, norm_whole ? nullptr : (is_q ? q_norm : k_norm), eps, 0, rot_dims, rotation, lane);
         if (is_q) {
             T* dst = q_out + ((size_t)t * nq + head) * d;
             for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(h[i]);
@@ -173,15 +192,17 @@ latent_prepare_kernel(const float* __restrict__ q_rows, long long ld_q, const fl
 }  // namespace
 
 // rows [n, ld] 32-bit: nq heads of d, nkv heads of d, nkv heads of dv.  bias (32-bit, the rows' layout) or null;
-// q_norm, k_norm (32-bit [d]) or null; freq (32-bit [rot_dims / 2]; rot_dims 0: no encoding).  vmix_mode 1 writes,
+// q_norm, k_norm (32-bit [d]; with `norm_whole` [nq d] and [nkv d]: one norm over all of q and one over all of k) or
+// null; freq (32-bit [rot_dims / 2]; rot_dims 0: no encoding).  vmix_mode 1 writes,
 // 2 reads v_first (32-bit [n, nkv dv]).  q_out [n, nq d], k_pages [pages, page_size, nkv, d], v_pages [.., nkv, dv].
 LIA_EXPORT int lia_qkv_prepare(const float* rows, long long ld, const float* bias, const float* q_norm,
                                const float* k_norm, float eps, const float* freq, int rot_dims, int vmix_mode,
                                float lambda, float* v_first, const int* positions, const int* slots,
                                const int* block_table, int table_stride, void* q_out, void* k_pages, void* v_pages,
                                int dtype, int n_tokens, int nq, int nkv, int d, int dv, int page_size, int num_pages,
-                               int write_kv, int* error_flag, cudaStream_t stream) {
+                               int write_kv, int norm_whole, int* error_flag, cudaStream_t stream) {
     if (n_tokens <= 0) return LIA_OK;
+    if (norm_whole && (!q_norm || !k_norm)) return LIA_ERR_SIZE;
     if (nq <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || page_size <= 0 || rot_dims < 0 || rot_dims > d || (rot_dims & 1) ||
         (rot_dims > 0 && !freq) || ld < (long long)(nq + nkv) * d + (long long)nkv * dv || vmix_mode < 0 || vmix_mode > 2 ||
         (vmix_mode && !v_first) || d > 4096)
@@ -191,7 +212,7 @@ LIA_EXPORT int lia_qkv_prepare(const float* rows, long long ld, const float* bia
     return lia_launch(qkv_prepare_kernel<T>, dim3(n_tokens), dim3(PREP_WARPS * 32), smem, stream, rows, ld, bias,     \
                       q_norm, k_norm, eps, freq, rot_dims, vmix_mode, lambda, v_first, positions, slots, block_table, \
                       table_stride, (T*)q_out, (T*)k_pages, (T*)v_pages, n_tokens, nq, nkv, d, dv, page_size,         \
-                      num_pages, write_kv, error_flag)
+                      num_pages, write_kv, norm_whole, error_flag)
     if (dtype == LIA_BF16) LIA_PREP(__nv_bfloat16);
     if (dtype == LIA_F32) LIA_PREP(float);
 #undef LIA_PREP

@@ -40,6 +40,7 @@ def lib():
 class _Signatures:
     lia_embedding = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
     lia_rmsnorm = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p]
+    lia_layernorm = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
     lia_rope_kv_write = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                          c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
     lia_gemm_simt = [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,
@@ -95,14 +96,14 @@ class _Signatures:
 
     lia_norm_residual = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float,
                          c_void_p]
-    lia_activation_rows = [c_void_p, ctypes.c_longlong, c_void_p, c_int, ctypes.c_longlong, c_int, c_int, c_int, c_void_p]
+    lia_activation_rows = [c_void_p, ctypes.c_longlong, c_void_p, c_int, ctypes.c_longlong, c_int, c_int, c_int, c_int, c_void_p]
     lia_attention_general = [c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_void_p, ctypes.c_longlong, ctypes.c_longlong,
                              c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                              c_int, c_void_p, c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_int, c_int, c_int, c_int,
-                             c_int, c_float, c_int, c_int, c_void_p, c_void_p]
+                             c_int, c_float, c_float, c_int, c_int, c_void_p, c_void_p]
     lia_qkv_prepare = [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_float,
                        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     lia_latent_prepare = [c_void_p, ctypes.c_longlong, c_void_p, ctypes.c_longlong, c_void_p, c_float, c_void_p, c_int,
                           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
@@ -125,18 +126,22 @@ class _Signatures:
     lia_hyper_step = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                       c_int, c_int, c_float, c_void_p]
     lia_softcap_rows = [c_void_p, ctypes.c_longlong, c_int, c_int, c_float, c_void_p]
-    lia_gate_rows = [c_void_p, c_int, ctypes.c_longlong, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_void_p]
+    lia_gate_rows = [c_void_p, c_int, ctypes.c_longlong, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_int, c_void_p]
     lia_moe_tile_rows = []
     lia_moe_route = [c_void_p, c_int, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
-                     c_void_p, c_void_p, c_void_p]
+                     c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     lia_moe_plan = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
     lia_moe_gather = [c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
     lia_moe_gemm = [c_int, c_void_p, c_int, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong,
                     c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     lia_gemm_tc_grouped = [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
-    lia_moe_combine = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int,
-                       c_void_p]
+    lia_moe_combine = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, ctypes.c_longlong,
+                       c_int, c_int, c_int, c_float, c_int, c_void_p]
+    lia_gla_encode = [c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                      c_int, c_float, c_float, c_void_p]
+    lia_gla = [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_void_p, c_int,
+               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, ctypes.c_longlong, c_void_p]
     lia_retention_chunks = [c_int, c_int]
     lia_retention_encode = [c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                             c_void_p]
@@ -279,6 +284,18 @@ def rmsnorm(x, weight, out, eps: float, out_scale: float = 1.0, rows_index=None)
     with _timed("rmsnorm"):
         _check(lib().lia_rmsnorm(_p(x), _p(rows_index), _p(weight), dtype_code(weight.dtype), _p(out),
                                  dtype_code(out.dtype), rows, hidden, eps, out_scale, _stream()), "rmsnorm")
+
+
+def layernorm(x, weight, bias, out, eps: float, rows_index=None):
+    """out[r] = (x[r] - mean) / sqrt(mean((x[r] - mean)^2) + eps) * weight + bias (bias may be None); x 32-bit rows, row
+    r taken from rows_index[r] when an index is given; see csrc/elementwise.cu."""
+    _cuda(x, weight, bias, out, rows_index)
+    rows, hidden = out.shape
+    if x.dtype != torch.float32 or x.shape[1] != hidden or (bias is not None and bias.dtype != weight.dtype):
+        raise KernelError("layernorm takes 32-bit rows of the same width as its output, weight and bias of one element type")
+    with _timed("layernorm"):
+        _check(lib().lia_layernorm(_p(x), _p(rows_index), _p(weight), _p(bias), dtype_code(weight.dtype), _p(out),
+                                   dtype_code(out.dtype), rows, hidden, float(eps), _stream()), "layernorm")
 
 
 def rope_kv_write(qkv, positions, slots, block_table, q_out, k_pages, v_pages, nq, nkv, d, rotary_dim,
@@ -827,7 +844,7 @@ def sigmoid_attention_tc(q, k_pages, v_pages, segments, n_segments, portion_tile
 # ---- parts of decoders with a norm on both sides of a sublayer, attention through a latent, attention with a sink,
 # ---- and a recurrent mixer with input-dependent decay
 
-ACT_NONE, ACT_GELU_TANH, ACT_SILU = 0, 1, 2
+ACT_NONE, ACT_GELU_TANH, ACT_SILU, ACT_RELU_SQUARED, ACT_RELU = 0, 1, 2, 3, 4
 
 
 def _f32(*tensors):
@@ -851,22 +868,26 @@ def norm_residual(y, weight, residual, eps: float, bias=None, next_weight=None, 
                                        next_eps, _stream()), "norm_residual")
 
 
-def activation_rows(source, out, act: int = ACT_NONE):
-    """out[r, :] = act(source[r, :]) for 32-bit rows `source` (any row stride); see csrc/norm_residual.cu."""
+def activation_rows(source, out, act: int = ACT_NONE, gated: bool = False):
+    """out[r, :] = act(source[r, :]) for 32-bit rows `source` (any row stride); with `gated` the rows hold a gate half and
+    then another half of out's width, out = act(gate) * the other half; see csrc/norm_residual.cu."""
     if not (source.is_cuda and out.is_cuda) or source.dtype != torch.float32 or source.dim() != 2 or out.dim() != 2 or \
-            source.shape != out.shape or source.stride(1) != 1 or out.stride(1) != 1:
-        raise KernelError("activation_rows: 32-bit rows in, rows of the same shape out")
+            source.shape[0] != out.shape[0] or source.shape[1] != (2 if gated else 1) * out.shape[1] or \
+            source.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("activation_rows: 32-bit rows in, rows of the same shape (gated: of half the width) out")
     with _timed("activation_rows", nbytes=source.numel() * 4 + out.numel() * out.element_size()):
         _check(lib().lia_activation_rows(_p(source), source.stride(0), _p(out), dtype_code(out.dtype), out.stride(0),
-                                         source.shape[0], source.shape[1], int(act), _stream()), "activation_rows")
+                                         out.shape[0], out.shape[1], int(act), 1 if gated else 0, _stream()),
+               "activation_rows")
 
 
 def attention_general(q1, q1_strides, q2, q2_strides, k1_pages, k2_pages, v_pages, v_stride, dv, positions, slots,
                       block_table, out, out_strides, n_tokens, nq, nkv, window, scale, sink=False, rows=None,
-                      error_flag=None, label=None, work_bytes=0):
+                      error_flag=None, label=None, work_bytes=0, softcap=None):
     """Softmax attention whose keys come in up to two parts (k1 [pages, page, nkv, dk1] with q1, k2 [.., dk2] with q2; k2
     and q2 may be None) and whose values are the first `dv` of every `v_stride` elements of `v_pages`; q1, q2 and out
-    are addressed by (token stride, head stride) in elements; `sink` adds one to the denominator; see
+    are addressed by (token stride, head stride) in elements; `sink` adds one to the denominator; `softcap`: the scores
+    pass cap * tanh(score / cap) ahead of the softmax; see
     csrc/attention_generic.cu.  For every token of the batch, or for the batch indices `rows`."""
     _cuda(k1_pages, k2_pages, v_pages, positions, slots, block_table, rows, error_flag)
     for t in (q1, q2, out):
@@ -884,14 +905,15 @@ def attention_general(q1, q1_strides, q2, q2_strides, k1_pages, k2_pages, v_page
                                            _p(k2_pages), dk2, _p(v_pages), int(v_stride), int(dv), dtype_code(q1.dtype),
                                            _p(positions), _p(slots), _p(block_table), block_table.shape[1], _p(rows),
                                            _p(out), out_strides[0], out_strides[1], n, nq, nkv, k1_pages.shape[1],
-                                           int(window or 0), scale, 1 if sink else 0, k1_pages.shape[0], _p(error_flag),
+                                           int(window or 0), scale, float(softcap or 0.0), 1 if sink else 0, k1_pages.shape[0], _p(error_flag),
                                            _stream()), "attention_general")
 
 
 def qkv_prepare(rows, bias, q_norm, k_norm, eps, freq, rot_dims, vmix_mode, vmix_lambda, v_first, positions, slots,
-                block_table, q_out, k_pages, v_pages, nq, nkv, d, dv, write_kv=True, error_flag=None):
+                block_table, q_out, k_pages, v_pages, nq, nkv, d, dv, write_kv=True, error_flag=None, norm_whole=False):
     """Bias, per-head RMS norm of q and k, rotate-half encoding, value mixing and the append to the pages for the
-    32-bit rows [q | k | v] of a product; see csrc/qk_prepare.cu."""
+    32-bit rows [q | k | v] of a product; see csrc/qk_prepare.cu.  `norm_whole`: one RMS norm over all of q's elements and
+    one over all of k's instead (weights [nq d] and [nkv d])."""
     _cuda(bias, q_norm, k_norm, freq, v_first, positions, slots, block_table, q_out, k_pages, v_pages, error_flag)
     _f32(rows, bias, q_norm, k_norm, freq, v_first)
     if not rows.is_cuda or rows.stride(1) != 1 or rows.shape[1] < (nq + nkv) * d + nkv * dv:
@@ -904,7 +926,8 @@ def qkv_prepare(rows, bias, q_norm, k_norm, eps, freq, rot_dims, vmix_mode, vmix
                                      int(rot_dims), int(vmix_mode), float(vmix_lambda), _p(v_first), _p(positions),
                                      _p(slots), _p(block_table), block_table.shape[1], _p(q_out), _p(k_pages), _p(v_pages),
                                      dtype_code(q_out.dtype), rows.shape[0], nq, nkv, d, dv, k_pages.shape[1],
-                                     k_pages.shape[0], 1 if write_kv else 0, _p(error_flag), _stream()), "qkv_prepare")
+                                     k_pages.shape[0], 1 if write_kv else 0, 1 if norm_whole else 0, _p(error_flag), _stream()),
+               "qkv_prepare")
 
 
 def latent_prepare(q_rows, shared_rows, latent_norm, eps, freq, rot_dims, positions, slots, block_table, q_plain,
@@ -1125,16 +1148,17 @@ def softcap_rows(z, cap: float):
         _check(lib().lia_softcap_rows(_p(z), z.stride(0), z.shape[0], z.shape[1], float(cap), _stream()), "softcap_rows")
 
 
-def gate_rows(o, g, act: int):
-    """o <- o * f(g) element by element, f the logistic function (`GATE_SIGMOID`) or SiLU (`GATE_SILU`); g 32-bit rows (a
-    slice of wider rows will do), o rows of the compute element type."""
+def gate_rows(o, g, act: int, span: int = 1):
+    """o[r, i] <- o[r, i] * f(g[r, i // span]), f the logistic function (`GATE_SIGMOID`) or SiLU (`GATE_SILU`); g 32-bit
+    rows (a slice of wider rows will do), o rows of the compute element type.  span 1: element by element; span = a
+    head's size: one gate a head."""
     _f32(g)
     if not (o.is_cuda and g.is_cuda) or o.dim() != 2 or g.dim() != 2 or o.stride(1) != 1 or g.stride(1) != 1 or \
-            tuple(o.shape) != tuple(g.shape):
-        raise KernelError("gate_rows: rows of one shape")
+            o.shape[0] != g.shape[0] or o.shape[1] != g.shape[1] * int(span):
+        raise KernelError("gate_rows: o's rows are span times as wide as g's")
     with _timed("gate_rows"):
         _check(lib().lia_gate_rows(_p(o), dtype_code(o.dtype), o.stride(0), _p(g), g.stride(0), o.shape[0], o.shape[1],
-                                   int(act), _stream()), "gate_rows")
+                                   int(act), int(span), _stream()), "gate_rows")
 
 
 # ---- a mixture of gated experts: csrc/moe.cu ----
@@ -1169,11 +1193,14 @@ def moe_grouped_accepts(x, w_gate_up, w_down) -> bool:
             w_down.data_ptr() % 16 == 0)
 
 
-def moe_route(x, router, top: int, scale: float, ids, weights, shared_gate=None):
+def moe_route(x, router, top: int, scale: float, ids, weights, shared_gate=None, correction=None, groups: int = 0,
+              keep: int = 0, renormalise: bool = False):
     """Router scores in 32-bit, the `top` largest chosen: ids, weights [n, top]; with one more row in `router` than
-    experts, shared_gate [n] = the logistic function of that row's product."""
-    _cuda(x, router, ids, weights, shared_gate)
-    _f32(router, weights, shared_gate)
+    outputs, shared_gate [n] = the logistic function of that row's product.  `correction` [outputs] is added to the
+    scores for the choice only; `groups`/`keep`: only outputs of the best `keep` of `groups` equal groups can be chosen;
+    `renormalise`: the weights are divided by their sum."""
+    _cuda(x, router, ids, weights, shared_gate, correction)
+    _f32(router, weights, shared_gate, correction)
     n, hidden = x.shape
     extra = 0 if shared_gate is None else 1
     experts = router.shape[0] - extra
@@ -1181,7 +1208,8 @@ def moe_route(x, router, top: int, scale: float, ids, weights, shared_gate=None)
         raise KernelError("moe_route: shapes do not agree")
     with _timed("moe_route"):
         _check(lib().lia_moe_route(_p(x), dtype_code(x.dtype), x.stride(0), _p(router), n, hidden, experts, int(top),
-                                   float(scale), extra, _p(ids), _p(weights), _p(shared_gate), _stream()), "moe_route")
+                                   float(scale), extra, _p(correction), int(groups), int(keep), 1 if renormalise else 0,
+                                   _p(ids), _p(weights), _p(shared_gate), _stream()), "moe_route")
 
 
 def moe_plan(ids, experts: int, offsets, order, inverse, tiles, n_tiles, tile_rows: int = 0, pad: bool = False):
@@ -1212,18 +1240,20 @@ def moe_gather(x, order, top: int, out):
                "moe_gather")
 
 
-def moe_gemm(gated: bool, a, order, top: int, w, out, tiles, n_tiles, max_tiles: int, label=None):
-    """The experts' products over the planned tiles, on the 32-bit pipes.  `gated`: a = the tokens' rows, read through
-    `order`; w [experts, 2 N, K] = [gate; up]; out [pairs, N] = up * silu(gate) in the compute element type.  Else a =
-    sorted rows [pairs, K], w [experts, N, K], out [pairs, N] 32-bit."""
+def moe_gemm(gated, a, order, top: int, w, out, tiles, n_tiles, max_tiles: int, label=None):
+    """The experts' products over the planned tiles, on the 32-bit pipes.  `gated` True (1): a = the tokens' rows, read
+    through `order`; w [experts, 2 N, K] = [gate; up]; out [pairs, N] = up * silu(gate) in the compute element type.
+    `gated` 2: a likewise, w [experts, N, K], out = relu(a w^T)^2 in the compute element type.  Else a = sorted rows
+    [pairs, K], w [experts, N, K], out [pairs, N] 32-bit."""
     _cuda(a, order, w, out, tiles, n_tiles)
     N, K = out.shape[1], a.shape[1]
-    if w.dim() != 3 or w.shape[1] != (2 * N if gated else N) or w.shape[2] != K or a.dtype != w.dtype or \
+    gated = int(gated)
+    if w.dim() != 3 or w.shape[1] != (2 * N if gated == 1 else N) or w.shape[2] != K or a.dtype != w.dtype or \
             out.dtype != (a.dtype if gated else torch.float32):
         raise KernelError("moe_gemm: shapes or element types do not agree")
     pairs = out.shape[0]
     with _timed("moe_gemm", label, nbytes=w.numel() * w.element_size(), flops=2 * pairs * w.shape[1] * K):
-        _check(lib().lia_moe_gemm(1 if gated else 0, _p(a), dtype_code(a.dtype), a.stride(0), _p(order), int(top), _p(w),
+        _check(lib().lia_moe_gemm(gated, _p(a), dtype_code(a.dtype), a.stride(0), _p(order), int(top), _p(w),
                                   _p(out), out.stride(0), _p(tiles), _p(n_tiles), int(max_tiles), N, K, _stream()), "moe_gemm")
 
 
@@ -1244,13 +1274,15 @@ def gemm_tc_grouped(mode, a, w, out, tile_rows: int, tiles, n_tiles, max_tiles: 
                                          _p(error_flag), _stream()), "gemm_tc_grouped")
 
 
-def moe_combine(residual, y, inverse, weights, shared_y, shared_gate, top: int, alpha: float, store: bool):
-    """residual (+)= alpha * (sum_c weights[t, c] y[inverse[t, c]] + shared_gate[t] shared_y[t])."""
-    _cuda(residual, y, inverse, weights, shared_y, shared_gate)
+def moe_combine(residual, y, inverse, weights, shared_y, shared_gate, top: int, alpha: float, store: bool, x=None):
+    """residual (+)= alpha * (sum_c weights[t, c] y[inverse[t, c]] + shared_gate[t] shared_y[t]); a choice without a row
+    (inverse < 0: an identity output) adds weights[t, c] x[t], x the tokens' inputs [n, hidden]."""
+    _cuda(residual, y, inverse, weights, shared_y, shared_gate, x)
     _f32(residual, y, weights, shared_y, shared_gate)
     n, hidden = residual.shape
     with _timed("moe_combine"):
-        _check(lib().lia_moe_combine(_p(residual), _p(y), _p(inverse), _p(weights), _p(shared_y), _p(shared_gate), n, hidden,
+        _check(lib().lia_moe_combine(_p(residual), _p(y), _p(inverse), _p(weights), _p(shared_y), _p(shared_gate), _p(x),
+                                     F32 if x is None else dtype_code(x.dtype), 0 if x is None else x.stride(0), n, hidden,
                                      int(top), float(alpha), 1 if store else 0, _stream()), "moe_combine")
 
 
@@ -1293,3 +1325,45 @@ def retention(rows, decay, state, segments, n_segments: int, max_chunks: int, si
                                    int(n_segments), int(max_chunks), _p(single_rows), n_single, _p(slots), _p(out),
                                    dtype_code(out.dtype), heads, d, dv, float(eps), _p(scratch),
                                    0 if scratch is None else scratch.numel(), _stream()), "retention")
+
+
+# ---- gated linear attention (a linear recurrence with a decay per token and key channel): csrc/gated_linear_attention.cu ----
+GLA_MAX_HEAD = 256
+
+
+def gla_scratch_floats(chunks: int, heads: int, d: int, dv: int) -> int:
+    return chunks * heads * d * (dv + 1)
+
+
+def gla_encode(rows, w_a2, bias, log_decay, slots, heads: int, d: int, dv: int, q_scale: float, tau: float):
+    """rows [n, >= 2 heads (d + dv) + rank] 32-bit = [q | k | v | g | a]: q times q_scale in place; log_decay [n, heads d]
+    32-bit = log2(sigmoid(w_a2 a + bias)) / tau."""
+    _cuda(w_a2, bias, log_decay, slots)
+    _f32(rows, bias, log_decay)
+    rank = w_a2.shape[1]
+    if rows.stride(1) != 1 or rows.shape[1] < 2 * heads * (d + dv) + rank or tuple(w_a2.shape) != (heads * d, rank) or \
+            not w_a2.is_contiguous() or tuple(log_decay.shape) != (rows.shape[0], heads * d) or not log_decay.is_contiguous():
+        raise KernelError("gla_encode: shapes do not agree")
+    with _timed("gla_encode"):
+        _check(lib().lia_gla_encode(_p(rows), rows.stride(0), _p(w_a2), dtype_code(w_a2.dtype), _p(bias), _p(log_decay),
+                                    _p(slots), rows.shape[0], heads, d, dv, rank, float(q_scale), float(tau), _stream()),
+               "gla_encode")
+
+
+def gla(rows, log_decay, state, segments, n_segments: int, max_chunks: int, single_rows, slots, norm_weight, out, heads: int,
+        d: int, dv: int, eps: float, scratch=None):
+    """S <- diag(alpha) S + k v^T, o = S^T q, out = o / rms(o) * norm_weight * silu(g) along the step's runs; rows
+    [n, 2 heads (d + dv) ..] 32-bit = [q | k | v | g ..] and log_decay = log2(alpha) as `gla_encode` left them, state
+    [slots, heads, d, dv] 32-bit."""
+    _cuda(log_decay, segments, single_rows, slots, norm_weight, out, scratch)
+    _f32(rows, log_decay, state, norm_weight, scratch)
+    n_single = 0 if single_rows is None else single_rows.numel()
+    if rows.stride(1) != 1 or rows.shape[1] < 2 * heads * (d + dv) or tuple(out.shape) != (rows.shape[0], heads * dv) or \
+            state[0].numel() != heads * d * dv or not state[0].is_contiguous() or \
+            tuple(log_decay.shape) != (rows.shape[0], heads * d) or not log_decay.is_contiguous():
+        raise KernelError("gla: shapes do not agree")
+    with _timed("gla", nbytes=rows.numel() * 4, flops=4 * rows.shape[0] * heads * d * dv):
+        _check(lib().lia_gla(_p(rows), rows.stride(0), _p(log_decay), _p(state), state.stride(0), _p(segments),
+                             int(n_segments), int(max_chunks), _p(single_rows), n_single, _p(slots), _p(norm_weight), _p(out),
+                             dtype_code(out.dtype), heads, d, dv, float(eps), _p(scratch),
+                             0 if scratch is None else scratch.numel(), _stream()), "gla")

@@ -3,7 +3,9 @@
 against [Wg; Wu] whose epilogue applies the activation (the reference's gated kernel does the
 same with two matrices: src/gpu/kernels/llama_gated.rs:181-222); the down product adds into the
 residual stream.  Parameters: hidden, intermediate, and optionally `names`: the checkpoint names of the gate, up
-and down matrices behind the part's prefix."""
+and down matrices behind the part's prefix, and `gate_activation`: "silu" (default) or "relu", act = up * relu(gate); the
+latter takes gate and up as 32-bit rows of the one product and applies the activation in a kernel of its own
+(csrc/norm_residual.cu)."""
 from __future__ import annotations
 
 import torch
@@ -41,18 +43,29 @@ class SwiGLU(FeedForward):
         gate, up, down = self._names(params, prefix)
         self.w_gate_up = prepare_weight(torch.cat([tensors[gate], tensors[up]], dim=0), runtime)
         self.w_down = prepare_weight(tensors[down], runtime)
+        self.relu = params.get("gate_activation", "silu") == "relu"
+
+    @staticmethod
+    def check_params(params):
+        if params.get("gate_activation", "silu") not in ("silu", "relu"):
+            raise ValueError("gated feed-forward: gate_activation is 'silu' or 'relu'")
 
     def forward(self, ctx, x, residual, scale, store=False):
         rt, n = self.runtime, x.shape[0]
         act = ctx.buffer("ffn.act", (n, self.intermediate), rt.compute_dtype)
-        linear(rt, SWIGLU, x, self.w_gate_up, act, error_flag=ctx.error_flag, name="gate_up")
+        if self.relu:
+            both = ctx.buffer("ffn.gate_up", (n, 2 * self.intermediate), torch.float32)
+            linear(rt, STORE, x, self.w_gate_up, both, error_flag=ctx.error_flag, name="gate_up")
+            rt.ops.activation_rows(both, act, rt.ops.ACT_RELU, gated=True)
+        else:
+            linear(rt, SWIGLU, x, self.w_gate_up, act, error_flag=ctx.error_flag, name="gate_up")
         linear(rt, STORE if store else ACCUM, act, self.w_down, residual, scale, error_flag=ctx.error_flag, name="down")
 
 
 @register_feed_forward("dense_act")
 class DenseActivation(FeedForward):
     """Dense feed-forward without a gate: f = Wd act(Wu x), no biases.  `activation`: "gelu_tanh"
-    (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))), "silu" or "none".  The activation is taken of the up product's
+    (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))), "silu", "relu_squared" (relu(z)^2), "relu" or "none".  The activation is taken of the up product's
     32-bit result and rounded once to the compute element type: in the product's epilogue where the kernel can (the
     few-token persistent product), else by a kernel of its own on the product's 32-bit rows; the down product adds into
     the residual stream.  Parameters: hidden, intermediate, activation, and optionally `names`: the checkpoint names of the up and
@@ -61,7 +74,7 @@ class DenseActivation(FeedForward):
     takes_deferred_norm = True
     can_store = True
     NAMES = {"up": "up_proj.weight", "down": "down_proj.weight"}
-    ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "silu": 2}
+    ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "silu": 2, "relu_squared": 3, "relu": 4}
 
     def graph_key(self, ctx) -> tuple:
         return ()

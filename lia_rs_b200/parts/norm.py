@@ -35,3 +35,40 @@ class RMSNorm(Norm):
 
     def rms_record(self):
         return self.weight, self.eps
+
+
+@register_norm("layernorm")
+class LayerNorm(Norm):
+    """Layer norm: y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b, mean and variance over the row in 32-bit
+    (csrc/elementwise.cu).  Parameters: hidden, eps, and optionally `tensor` and `bias_tensor`: what follows the norm's
+    prefix in the checkpoint names of weight and bias (defaults "weight" and "bias"); `bias_tensor` None: no bias.  It is
+    not an RMS norm, so no product kernel applies it (`rms_record` answers None) and it always runs its own kernel."""
+    graph_safe = True
+
+    def graph_key(self, ctx) -> tuple:
+        return ()
+
+    @staticmethod
+    def _names(params, prefix):
+        bias = params.get("bias_tensor", "bias")
+        return prefix + params.get("tensor", "weight"), None if bias is None else prefix + bias
+
+    @staticmethod
+    def tensor_specs(params, prefix):
+        weight, bias = LayerNorm._names(params, prefix)
+        specs = [TensorSpec(weight, (params["hidden"],), kind="norm")]
+        if bias is not None:
+            specs.append(TensorSpec(bias, (params["hidden"],)))
+        return specs
+
+    def __init__(self, params, tensors, prefix, runtime):
+        super().__init__(params, tensors, prefix, runtime)
+        self.hidden, self.eps = int(params["hidden"]), float(params["eps"])
+        weight, bias = self._names(params, prefix)
+        self.weight = tensors[weight].to(torch.float32).contiguous()
+        self.bias = None if bias is None else tensors[bias].to(torch.float32).contiguous()
+
+    def forward(self, ctx, x, out, rows_index=None, out_scale=1.0):
+        if out_scale != 1.0:
+            raise ValueError("layer norm: no output scale")
+        self.runtime.ops.layernorm(x, self.weight, self.bias, out, self.eps, rows_index)

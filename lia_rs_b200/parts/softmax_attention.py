@@ -2,7 +2,8 @@
 
 `sink_attention`: grouped-query attention, q = Wq x + bq, k = Wk x + bk, v = Wv x + bv (biases optional), with
   * an RMS norm of every q head and every k head over the head's elements, with one weight of the head's size for all
-    q heads and one for all k heads (optional), ahead of the rotation;
+    q heads and one for all k heads (optional; `qk_norm` "whole": one RMS norm over all of q's elements at once and one
+    over all of k's, with weights of those sizes), ahead of the rotation;
   * rotate-half encoding over the first `rot.dims` elements of a head, frequencies plain or scaled by wavelength bands
     (`rotary.band_scaled_frequencies`);
   * values of a head size of their own;
@@ -11,8 +12,10 @@
     mixed values are what the pages hold;
   * a sink (optional): one is added to the softmax's denominator, p_j = exp(s_j) / (1 + sum exp(s_j)), the weight of
     a key of score 0 that has no value;
+  * a cap on the scores (optional, `softcap`): s <- cap * tanh(s / cap) ahead of the softmax;
   * all keys j <= i, or the last `window` of them;
-  * an output projection whose bias (optional) is the mixer's `output_bias`.
+  * an output projection whose bias (optional; `biases` "qkv": the three input projections have biases and the output
+    projection none) is the mixer's `output_bias`.
 
 `latent_attention`: queries and keys go through latents.  c_q = rms(W_dq x) w; q = W_uq c_q, per head `head_dim`
 unrotated and `rot_dim` rotated elements.  W_dkv x gives `kv_rank` elements whose RMS norm (with a weight) is the latent
@@ -22,7 +25,8 @@ parts), so attention runs in the latent's space: the unrotated query is taken th
 q~_h = W_uk,h^T q_h, the score is scale (q~_h . c_j + q_rot,h . r_j), the weighted sum of the latents is taken through
 W_uv,h afterwards, and the heads side by side through W_o.  A window as above; no sink.  Options: `q_rank` None: the
 queries come straight from the input, q = W_q x; `rot_pairs`: the rotation pairs element 2i with 2i + 1 instead of i with
-i + dims / 2; `gate` "sigmoid": the heads side by side are multiplied by sigmoid(W_g x) ahead of W_o; `shared_cache`: the
+i + dims / 2; `gate` "sigmoid": the heads side by side are multiplied by sigmoid(W_g x) ahead of W_o ("sigmoid_head": W_g
+has one row a head, and a head's output is multiplied by that one number); `shared_cache`: the
 layer has no W_dkv and reads the latents and rotated parts that another layer of the same sizes and rotation put into the
 pages (the model's schedule names that layer's cache), with W_uk, W_uv and queries of its own.
 
@@ -86,6 +90,12 @@ class SinkAttention(Mixer):
             raise ValueError("attention: value_mix is None, 'source' or 'mixed'")
         if params.get("window") is not None and int(params["window"]) <= 0:
             raise ValueError("attention: window must be positive or None")
+        if params.get("softcap") is not None and not float(params["softcap"]) > 0:
+            raise ValueError("attention: softcap must be positive or None")
+        if params.get("biases") not in (None, False, True, "qkv") or params.get("qk_norm") not in (None, False, True, "whole"):
+            raise ValueError("attention: biases is absent, True or 'qkv'; qk_norm is absent, True or 'whole'")
+        if params.get("softcap") is not None and params.get("sink"):
+            raise ValueError("attention: a sink and a cap on the scores together are not built")
 
     @staticmethod
     def tensor_specs(params, prefix):
@@ -95,8 +105,12 @@ class SinkAttention(Mixer):
                  TensorSpec(n["o"], (h, nq * dv))]
         if params.get("biases"):
             specs += [TensorSpec(n["q_bias"], (nq * d,)), TensorSpec(n["k_bias"], (nkv * d,)),
-                      TensorSpec(n["v_bias"], (nkv * dv,)), TensorSpec(n["o_bias"], (h,))]
-        if params.get("qk_norm"):
+                      TensorSpec(n["v_bias"], (nkv * dv,))]
+            if params["biases"] != "qkv":
+                specs.append(TensorSpec(n["o_bias"], (h,)))
+        if params.get("qk_norm") == "whole":
+            specs += [TensorSpec(n["q_norm"], (nq * d,), kind="norm"), TensorSpec(n["k_norm"], (nkv * d,), kind="norm")]
+        elif params.get("qk_norm"):
             specs += [TensorSpec(n["q_norm"], (d,), kind="norm"), TensorSpec(n["k_norm"], (d,), kind="norm")]
         if params.get("value_mix"):
             specs.append(TensorSpec(n["mix"], ()))          # the first such layer stores one too and does not use it
@@ -128,7 +142,9 @@ class SinkAttention(Mixer):
         self.bias_in, self.output_bias = None, None
         if params.get("biases"):
             self.bias_in = f32(torch.cat([tensors[n["q_bias"]], tensors[n["k_bias"]], tensors[n["v_bias"]]]))
-            self.output_bias = f32(tensors[n["o_bias"]])
+            self.output_bias = f32(tensors[n["o_bias"]]) if params["biases"] != "qkv" else None
+        self.norm_whole = params.get("qk_norm") == "whole"
+        self.softcap = None if params.get("softcap") is None else float(params["softcap"])
         self.q_norm = f32(tensors[n["q_norm"]]) if params.get("qk_norm") else None
         self.k_norm = f32(tensors[n["k_norm"]]) if params.get("qk_norm") else None
         self.rot_dims, self.freq = _frequencies(params.get("rot"), device)
@@ -138,7 +154,7 @@ class SinkAttention(Mixer):
         # kernel for every size
         self.paged = None
         if runtime.compute_dtype == torch.bfloat16 and self.d == self.dv and self.d in ops.DECODE_HEAD_DIMS and \
-                self.nq // self.nkv <= 64:
+                self.nq // self.nkv <= 64 and self.softcap is None:
             self.paged = PagedAttention(runtime.compute_dtype, self.nq, self.nkv, self.d, self.window, self.scale, sink=self.sink)
 
     def graph_key(self, ctx) -> tuple:
@@ -154,14 +170,14 @@ class SinkAttention(Mixer):
         v_first = ctx.buffer("sinkattn.v_first", (n, nkv * dv), torch.float32) if self.mix_mode else None
         ops.qkv_prepare(projected, self.bias_in, self.q_norm, self.k_norm, self.eps, self.freq, self.rot_dims,
                         self.mix_mode, self.mix_lambda, v_first, ctx.positions, ctx.slots, kv.block_table, q, kv.k_pages,
-                        kv.v_pages, nq, nkv, d, dv, write_kv=kv.writes, error_flag=flag)
+                        kv.v_pages, nq, nkv, d, dv, write_kv=kv.writes, error_flag=flag, norm_whole=self.norm_whole)
         o = ctx.buffer("sinkattn.o", (n, nq * dv), rt.compute_dtype)
         if self.paged is not None:
             self.paged.forward(ctx, q, kv, o)
         else:
             ops.attention_general(q, (nq * d, d), None, None, kv.k_pages, None, kv.v_pages, dv, dv, ctx.positions, ctx.slots,
                                   kv.block_table, o, (nq * dv, dv), n, nq, nkv, self.window, self.scale, sink=self.sink,
-                                  error_flag=flag)
+                                  error_flag=flag, softcap=self.softcap)
         linear(rt, STORE if store else ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")
 
 
@@ -192,8 +208,8 @@ class LatentAttention(Mixer):
         _check_rot(params.get("rot"), int(params["rot_dim"]), "latent attention")
         if params.get("window") is not None and int(params["window"]) <= 0:
             raise ValueError("latent attention: window must be positive or None")
-        if params.get("gate") not in (None, "sigmoid"):
-            raise ValueError("latent attention: gate is None or 'sigmoid'")
+        if params.get("gate") not in (None, "sigmoid", "sigmoid_head"):
+            raise ValueError("latent attention: gate is None, 'sigmoid' or 'sigmoid_head'")
 
     @staticmethod
     def tensor_specs(params, prefix):
@@ -209,7 +225,7 @@ class LatentAttention(Mixer):
             specs += [TensorSpec(n["kv_down"], (rank + dr, h)), TensorSpec(n["kv_norm"], (rank,), kind="norm")]
         specs += [TensorSpec(n["k_up"], (H * d, rank)), TensorSpec(n["v_up"], (H * dv, rank))]
         if params.get("gate"):
-            specs.append(TensorSpec(n["gate"], (H * dv, h)))
+            specs.append(TensorSpec(n["gate"], (H if params["gate"] == "sigmoid_head" else H * dv, h)))
         return specs + [TensorSpec(n["o"], (h, H * dv))]
 
     @staticmethod
@@ -227,13 +243,14 @@ class LatentAttention(Mixer):
         self.scale, self.window = float(params["scale"]), params.get("window")
         self.eps = float(params.get("norm_eps", 1e-6))
         self.pairs, self.gated, self.own_cache = bool(params.get("rot_pairs")), bool(params.get("gate")), not params.get("shared_cache")
+        self.gate_span = int(params["v_head_dim"]) if params.get("gate") == "sigmoid_head" else 1
         n = self._names(params, prefix)
         H, d, dv, rank = self.heads, self.d, self.dv, self.rank
         # One product for everything that is read from the input beside a query latent: [W_q (queries straight from the
         # input) | W_dkv (a cache of the layer's own) | W_g (a gate)], padded with zero rows to a multiple of 8 columns.
         blocks, at, self.columns = [], 0, {}
         for key, present, rows in (("q", self.q_rank is None, H * (d + self.dr)), ("kv_down", self.own_cache, rank + self.dr),
-                                   ("gate", self.gated, H * dv)):
+                                   ("gate", self.gated, H * dv // self.gate_span)):
             if present:
                 blocks.append(tensors[n[key]])
                 self.columns[key] = (at, at + rows)
@@ -324,5 +341,5 @@ class LatentAttention(Mixer):
         o = ctx.buffer("latent.o", (n, H * dv), dtype)
         self._head_products(ctx, mixed, self.w_v_up, o.view(n, H, dv).transpose(0, 1), "v_up")
         if gate is not None:
-            ops.gate_rows(o, gate, ops.GATE_SIGMOID)
+            ops.gate_rows(o, gate, ops.GATE_SIGMOID, span=self.gate_span)
         linear(rt, STORE if store else ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")

@@ -53,6 +53,11 @@ def storage_dtype(dtype: torch.dtype) -> torch.dtype:
     return torch.int32
 
 
+def _fits(shape: tuple, wanted: tuple) -> bool:
+    """A dimension that the description leaves open (None: a size that only the stored tensor gives) fits any size."""
+    return len(shape) == len(wanted) and all(w is None or int(s) == int(w) for s, w in zip(shape, wanted))
+
+
 def _check_names_and_shapes(shapes: dict, specs) -> dict:
     """`shapes`: name -> shape of what is on offer.  Raises the one WeightError; returns name -> spec."""
     names = set(shapes)
@@ -60,7 +65,7 @@ def _check_names_and_shapes(shapes: dict, specs) -> dict:
     missing = [n for n, s in wanted.items() if n not in names and not s.optional]
     unexpected = sorted(names - set(wanted))
     wrong = [(name, spec.shape, tuple(shapes[name])) for name, spec in wanted.items()
-             if name in names and tuple(shapes[name]) != tuple(spec.shape)]
+             if name in names and not _fits(tuple(shapes[name]), tuple(spec.shape))]
     if missing or unexpected or wrong:
         raise WeightError(sorted(missing), unexpected, wrong)
     return wanted

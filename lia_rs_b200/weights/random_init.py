@@ -18,6 +18,8 @@ def random_tensors(specs, seed: int, std: float) -> dict:
     for spec in specs:
         if spec.optional:
             continue
+        if any(size is None for size in spec.shape):
+            raise ValueError(f"random weights: the size of {spec.name} is left to the stored tensor; the configuration must give it")
         if spec.kind == "norm":
             out[spec.name] = torch.ones(spec.shape, dtype=torch.bfloat16)
         elif spec.kind == "identity":
