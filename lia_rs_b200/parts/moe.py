@@ -55,7 +55,7 @@ class ExpertMixture(FeedForward):
     @staticmethod
     def check_params(params):
         experts, top = int(params["experts"]), int(params["top"])
-        if not 0 < experts <= ops.MOE_MAX_EXPERTS or not 0 < top <= min(experts, ops.MOE_MAX_TOP):
+        if not 0 < experts <= ops.MOE_MAX_EXPERTS or not 0 < top <= min(experts + int(params.get("identity") or 0), ops.MOE_MAX_TOP):
             raise ValueError(f"expert mixture: 1..{ops.MOE_MAX_EXPERTS} experts, of which 1..{ops.MOE_MAX_TOP} (at most all) "
                              "are chosen")
         if int(params["intermediate"]) <= 0 or (params.get("shared") and int(params["shared"]["intermediate"]) <= 0):

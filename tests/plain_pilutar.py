@@ -181,13 +181,13 @@ def route(h, w, router, fragile=None):
         c = c.masked_fill(~allowed.repeat_interleave(total // count, dim=1), float("-inf"))
         if fragile is not None and keep < count:
             ranked = torch.sort(best, dim=-1, descending=True).values
-            fragile |= (ranked[:, keep - 1] - ranked[:, keep]) < 2e-3
+            fragile |= (ranked[:, keep - 1] - ranked[:, keep]) < 1e-2
     chosen = torch.topk(c, top, dim=-1).indices
     if fragile is not None:
         ranked = torch.sort(c, dim=-1, descending=True).values
         if top < total:
             margin = ranked[:, top - 1] - ranked[:, top]
-            fragile |= margin < 2e-3          # (an excluded output's -inf gives an infinite margin)
+            fragile |= margin < 1e-2          # (an excluded output's -inf gives an infinite margin)
     picked = torch.gather(s, 1, chosen)
     return chosen, picked / (picked.sum(dim=-1, keepdim=True) + 1e-20)
 
