@@ -549,6 +549,45 @@ def zipelix_workload(steps, warmup) -> int:
                          ZIPELIX_SIZES, zipelix_pair, steps, warmup)
 
 
+# The Pilutar decoder beside the Zipelix and Llama decoders at equal sizes (--workload pilutar): four layers each.  Pilutar:
+# parallel layers under one layer norm; a capped grouped-query attention (window of 1,024, whole-projection norms) beside
+# gated linear attention with a dense ReLU-gated feed-forward, attention through latents (window of 1,024, a gate a head)
+# with a mixture of eight squared-ReLU experts and two identity outputs in two groups (two chosen, one shared expert), the
+# first kind with that mixture, the second with the dense feed-forward.  Zipelix (the closest model: latents, a linear
+# recurrence and a mixture) and Llama as in its own workload.
+PILUTAR_WINDOW = 1024
+
+
+def pilutar_pair(size: dict):
+    from lia_rs_b200.config import PilutarConfig
+    dense = {"kind": "dense", "ff": size["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": size["expert_ff"]}, "shared": {"ff": size["shared_ff"]},
+           "router": {"experts": size["experts"], "top": size["top"], "identity": 2, "groups": {"count": 2, "keep": 1}}}
+    latent = {"heads": size["heads"], "dim": size["dim"], "rot_dim": size["rot_dim"], "vdim": size["dim"],
+              "kv_rank": size["kv_rank"], "scale": (size["dim"] + size["rot_dim"]) ** -0.5, "mask": {"size": PILUTAR_WINDOW},
+              "rot": {"base": 10000.0, "dims": size["rot_dim"]}}
+    side_by_side = {
+        "left": {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["dim"],
+                 "scale": size["dim"] ** -0.5, "softcap": 30.0, "mask": {"size": PILUTAR_WINDOW},
+                 "rot": {"base": 50000.0, "dims": size["dim"] // 2}},
+        "right": {"heads": size["heads"], "dim": size["dim"] // 2, "vdim": size["dim"], "tau": 16.0, "rank": 16},
+        "left_scale": 0.6, "right_scale": 0.5}
+    pilutar = PilutarConfig.from_dict({
+        "architecture": "Pilutar", "vocab": 8192, "width": size["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": 16.0},
+        "logit_scale": 0.25,
+        "layers": [{"type": "parallel", "mixer": side_by_side, "mlp": dense},
+                   {"type": "latent_attention", "mixer": latent, "mlp": moe},
+                   {"type": "parallel", "mixer": side_by_side, "mlp": moe},
+                   {"type": "latent_attention", "mixer": latent, "mlp": dense}]})
+    others = zipelix_pair(size)
+    return {"pilutar": pilutar, "zipelix": others["zipelix"], "llama": others["llama"]}
+
+
+def pilutar_workload(steps, warmup) -> int:
+    return pair_workload("pilutar", "Pilutar beside the Zipelix and Llama decoders at equal sizes, four layers, bf16",
+                         ZIPELIX_SIZES, pilutar_pair, steps, warmup)
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -559,7 +598,7 @@ def main() -> int:
                         help="run fewer layers than the configuration's 40 (both numbers are reported)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-points", action="store_true", help="skip batch 1 and batch 64")
-    parser.add_argument("--workload", default=None, choices=["8b-decode", "8b-prefill", "0.5b-mixed", "nafevik", "vatunex", "zipelix"],
+    parser.add_argument("--workload", default=None, choices=["8b-decode", "8b-prefill", "0.5b-mixed", "nafevik", "vatunex", "zipelix", "pilutar"],
                         help="one of the family's other sizes on the workload it is quoted on (prints its own line)")
     parser.add_argument("--device-trace", action="store_true",
                         help="with --workload 0.5b-mixed: one more pass under a trace of the device's kernels; adds "
@@ -584,6 +623,8 @@ def main() -> int:
         return vatunex_workload(args.steps, args.warmup)
     if args.workload == "zipelix":
         return zipelix_workload(args.steps, args.warmup)
+    if args.workload == "pilutar":
+        return pilutar_workload(args.steps, args.warmup)
     if args.workload:
         return other_workload(args.workload, args.steps, args.warmup, trace=args.device_trace)
 

@@ -37,7 +37,8 @@ struct Params {
     float* partial;                  // [tokens, nq, n_splits, D] normalised outputs, then [tokens, nq, n_splits] log2-sum-exps
     int* counters;                   // [n_rows, gridDim.y], zero between launches; null: ranges are merged by a second kernel
     int n_tokens, table_stride, nq, nkv, page_size, page_shift, window, split_len, n_splits;
-    float scale_log2;                // softmax scale * log2(e)
+    float scale_log2;                // softmax scale * log2(e); with a cap on the scores: cap * log2(e)
+    float cap_in;                    // 0: no cap; else scale / cap: the score is cap * tanh(q.k * cap_in)
     // position encoding and cache append in the same kernel (qkv non-null): q is taken from qkv, rotated here;
     // the CTA of a token's last range also rotates its new key and appends key and value to their page
     const float* qkv;                // [tokens, (nq + 2 nkv) D] 32-bit
@@ -62,6 +63,12 @@ __device__ __forceinline__ int range_length(const Params& p, int span) {
     return (per + TILE_KEYS - 1) / TILE_KEYS * TILE_KEYS;
 }
 
+// tanh by the hardware's approximation (relative error about 2^-11, below the rounding of the 16-bit probabilities)
+__device__ __forceinline__ float tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -425,6 +432,10 @@ attention_decode_kernel(Params p) {
             for (int h = 0; h < NH; ++h) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) st[h][i] += st_odd[h][i];
+                if (p.cap_in != 0.f) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) st[h][i] = tanh_approx(st[h][i] * p.cap_in);
+                }
                 if (low_hidden) st[h][0] = st[h][1] = -INFINITY;       // (only the range's last keys can be)
                 if (high_hidden) st[h][2] = st[h][3] = -INFINITY;
                 float correction[2], e[4];
@@ -840,8 +851,8 @@ LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const vo
                                     int table_stride, void* out, float* partial, long long partial_floats,
                                     int* counters, int n_tokens, int nq, int nkv, int d, int page_size, int window, float scale,
                                     int split_len, int n_splits, const float* qkv, const float* inv_freq, int rotary_dim,
-                                    int write_kv, int num_pages, int cluster, int all_new, int sink, int* error_flag,
-                                    cudaStream_t stream) {
+                                    int write_kv, int num_pages, int cluster, int all_new, int sink, float softcap,
+                                    int* error_flag, cudaStream_t stream) {
     if (n_rows <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || split_len < 0 || split_len % TILE_KEYS || n_splits <= 0 ||
         n_splits > 65535)
@@ -868,6 +879,11 @@ LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const vo
         if (page_size == (1 << b)) p.page_shift = b;
     p.n_tokens = n_tokens; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window;
     p.split_len = split_len; p.n_splits = n_splits; p.scale_log2 = scale * LOG2E;
+    p.cap_in = 0.f;
+    if (softcap > 0.f) {                 // scores cap * tanh(scale q.k / cap): the tanh's result times cap * log2(e)
+        p.cap_in = scale / softcap;
+        p.scale_log2 = softcap * LOG2E;
+    }
     const bool wide = nq / nkv > 8;             // more than 8 query heads per kv head: two groups of 8 per CTA
     if (d == 128) return wide ? launch_decode<128, 2>(p, n_rows, stream) : launch_decode<128, 1>(p, n_rows, stream);
     if (d == 64) return wide ? launch_decode<64, 2>(p, n_rows, stream) : launch_decode<64, 1>(p, n_rows, stream);

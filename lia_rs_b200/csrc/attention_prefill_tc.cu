@@ -58,7 +58,8 @@ struct Params {
     const int* block_table;          // [slots, table_stride]
     __nv_bfloat16* out;              // [tokens, nq, D]
     int n_segments, table_stride, nq, nkv, page_size, page_shift, window, tokens_per_tile;
-    float scale_log2;
+    float scale_log2;                // softmax scale * log2(e); with a cap on the scores: cap * log2(e)
+    float cap_in;                    // 0: no cap; else scale / cap: the score is cap * tanh(q.k * cap_in)
     int num_pages;
     int* error_flag;
     // With `splits` > 1 the keys of every CTA's rows are cut into that many ranges (blockIdx.z; whole tiles): each
@@ -267,6 +268,10 @@ attention_prefill_tc_kernel(Params p) {
             uint32_t raw[HALF];
             tmem_load64_nowait(tmem_s + (uint32_t)((j & 1) * KT + half * HALF) + lane_base, raw);
             tmem_load_wait();
+            if (p.cap_in != 0.f) {
+#pragma unroll
+                for (int c = 0; c < HALF; ++c) raw[c] = __float_as_uint(tanh_approx(__uint_as_float(raw[c]) * p.cap_in));
+            }
             if (masked) {
 #pragma unroll
                 for (int c = 0; c < HALF; ++c) {
@@ -503,7 +508,7 @@ LIA_EXPORT int lia_attention_prefill_tc(const void* q, const void* k_pages, cons
                                         int n_segments, int n_tiles, const int* slots, const int* block_table,
                                         int table_stride, void* out, int nq, int nkv, int d, int page_size, int window,
                                         float scale, int num_pages, int splits, float* partial, int n_tokens, int sink,
-                                        int* error_flag, cudaStream_t stream) {
+                                        float softcap, int* error_flag, cudaStream_t stream) {
     if (n_segments <= 0 || n_tiles <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || nkv > 65535) return LIA_ERR_SIZE;
     if (splits < 1 || splits > 32 || (splits > 1 && (!partial || n_tokens <= 0))) return LIA_ERR_SIZE;
@@ -518,6 +523,11 @@ LIA_EXPORT int lia_attention_prefill_tc(const void* q, const void* k_pages, cons
     p.n_segments = n_segments; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size;
     p.window = window; p.tokens_per_tile = per_tile; p.scale_log2 = scale * LOG2E; p.error_flag = error_flag;
     p.num_pages = num_pages;
+    p.cap_in = 0.f;
+    if (softcap > 0.f) {                 // scores cap * tanh(scale q.k / cap): the tanh's result times cap * log2(e)
+        p.cap_in = scale / softcap;
+        p.scale_log2 = softcap * LOG2E;
+    }
     p.page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if (page_size == (1 << b)) p.page_shift = b;

@@ -5,6 +5,12 @@
 #include "tcgen05.cuh"
 
 namespace tc5 {
+// tanh by the hardware's approximation (relative error about 2^-11, below the rounding of the 16-bit probabilities)
+__device__ __forceinline__ float tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

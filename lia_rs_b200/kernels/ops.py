@@ -52,7 +52,7 @@ class _Signatures:
     lia_wait_probe = [c_int, c_void_p, c_void_p, c_void_p]
     lia_attention_decode = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                            c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+                            c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
     lia_attention_decode_cluster_splits = [c_int, c_int, c_int, c_int]
     lia_attention_decode_ctas_per_sm = [c_int, c_int]
     lia_gemm_tc = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -69,7 +69,7 @@ class _Signatures:
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
     lia_attention_prefill_tc = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_int,
-                                c_void_p, c_void_p]
+                                c_float, c_void_p, c_void_p]
     lia_attention_prefill_tc_tokens_per_tile = [c_int, c_int]
     lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                          ctypes.c_longlong, c_void_p]
@@ -520,7 +520,7 @@ DECODE_HEAD_DIMS = (32, 64, 128)       # head sizes the tensor-core attention ke
 
 def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, nq, nkv, d, window,
                      scale, split_len, n_splits, counters=None, qkv=None, inv_freq=None, rotary_dim=0, write_kv=True,
-                     error_flag=None, label=None, work_bytes=0, cluster=False, all_new=False, sink=False):
+                     error_flag=None, label=None, work_bytes=0, cluster=False, all_new=False, sink=False, softcap=None):
     """Split-key decode attention (bfloat16) for the single-token rows of the batch; see
     csrc/attention_decode.cu.  `partial` is 32-bit scratch for the ranges' partial results.
     `split_len` 0: every row cuts its own visible span into `n_splits` ranges.  `counters` (int32, at
@@ -534,7 +534,8 @@ def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, o
     `partial` nor `counters` is used.  `all_new`: the rows may be tokens of this step's prompt portions, so any of
     their keys may have been written by the kernels ahead (otherwise only a row's own key is taken to be of this step,
     and the kernel fetches older tiles before it waits for those kernels).  `sink`: one is added to the softmax's denominator
-    (a key of score 0 without a value), once, where a token's ranges meet."""
+    (a key of score 0 without a value), once, where a token's ranges meet.  `softcap`: the scores pass
+    cap * tanh(score / cap) ahead of the softmax (the hardware's tanh approximation)."""
     _cuda(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, counters, qkv, inv_freq, error_flag)
     if qkv is not None:
         if qkv.dtype != torch.float32 or qkv.shape[1] != (nq + 2 * nkv) * d:
@@ -551,7 +552,7 @@ def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, o
                                           0 if partial is None else partial.numel(), _p(counters), q.shape[0], nq, nkv, d,
                                           k_pages.shape[1], int(window or 0), scale, split_len, n_splits, _p(qkv), _p(inv_freq),
                                           int(rotary_dim), 1 if write_kv else 0, k_pages.shape[0], 1 if cluster else 0, 1 if all_new else 0,
-                                          1 if sink else 0, _p(error_flag),
+                                          1 if sink else 0, float(softcap or 0.0), _p(error_flag),
                                           _stream()),
                "attention_decode")
 
@@ -593,7 +594,8 @@ def attention_prefill_tc_tokens_per_tile(group: int, d: int) -> int:
 
 
 def attention_prefill_tc(q, k_pages, v_pages, segments, n_segments, n_tiles, slots, block_table, out, nq, nkv, d,
-                         window, scale, error_flag=None, label=None, work_flops=0, splits=1, partial=None, sink=False):
+                         window, scale, error_flag=None, label=None, work_flops=0, splits=1, partial=None, sink=False,
+                         softcap=None):
     """Prompt-portion attention on the tcgen05 tensor cores (bfloat16, head size 64 or 128, heads per kv head a
     divisor of 128); see csrc/attention_prefill_tc.cu.  Arguments as `attention_prefill`.  `splits` > 1 cuts every
     CTA's keys into that many ranges that run side by side and are merged by a second kernel; `partial` is their
@@ -610,7 +612,7 @@ def attention_prefill_tc(q, k_pages, v_pages, segments, n_segments, n_tiles, slo
                                               _p(slots), _p(block_table), block_table.shape[1], _p(out), nq, nkv, d,
                                               k_pages.shape[1], int(window or 0), scale, k_pages.shape[0], splits,
                                               _p(partial) if splits > 1 else None, q.shape[0], 1 if sink else 0,
-                                              _p(error_flag), _stream()),
+                                              float(softcap or 0.0), _p(error_flag), _stream()),
                "attention_prefill_tc")
 
 

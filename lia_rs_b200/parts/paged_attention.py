@@ -36,26 +36,31 @@ class PagedAttention:
                              f"most {ops.ATTENTION_HEAD_DIM_MAX} (what the attention kernels take)")
 
     def __init__(self, dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, window, scale: float,
-                 rotate_half=None, sink: bool = False):
+                 rotate_half=None, sink: bool = False, softcap=None):
         """`rotate_half`: what the mixer's position encoding answers to `rotate_half()`; with it (and the
         tensor variant, and at most 16 query heads per kv head) decode-only steps encode, append and attend in
         one kernel (`forward_fused`).  `sink`: one is added to the softmax's denominator (the weight of a key of score 0
         that has no value); the tensor variant's kernels take it, the kernel for every size behind this class does not
-        (`ops.attention_general` does)."""
+        (`ops.attention_general` does).  `softcap`: the scores pass cap * tanh(score / cap) ahead of the softmax; the split-key
+        kernel and the tcgen05 prompt kernel take it (prompt portions whose group the tcgen05 kernel does not take go to
+        `ops.attention_general`), and the fused single-token step is not used."""
         self.check(heads, kv_heads, head_dim)
         self.sink = bool(sink)
+        self.softcap = None if softcap is None else float(softcap)
         self.nq, self.nkv, self.d = int(heads), int(kv_heads), int(head_dim)
         self.window, self.scale = window, float(scale)
         self.group = self.nq // self.nkv
         self.variant = "tensor" if dtype == torch.bfloat16 and self.d in ops.DECODE_HEAD_DIMS else "generic"
-        if self.sink and (self.variant != "tensor" or self.nq // self.nkv > 64):
-            raise ValueError("attention with a sink: only the tensor-core kernels behind this class take one")
+        if (self.sink or self.softcap) and (self.variant != "tensor" or self.nq // self.nkv > 64):
+            raise ValueError("attention with a sink or a cap: only the tensor-core kernels behind this class take one")
+        if self.sink and self.softcap:
+            raise ValueError("attention: a sink and a cap together are not built")
         if dtype == torch.bfloat16 and self.variant == "generic" and self.d not in _told:
             _told.add(self.d)
             print(f"[lia_rs_b200] bfloat16 attention with head size {self.d} runs on the kernel for every size "
                   f"(32-bit probabilities, a warp per token and head); the tensor-core kernels take "
                   f"{ops.DECODE_HEAD_DIMS}", file=sys.stderr, flush=True)
-        self.rotate_half = rotate_half if (self.variant == "tensor" and self.group <= 16) else None
+        self.rotate_half = rotate_half if (self.variant == "tensor" and self.group <= 16 and not self.softcap) else None
         self._prefill = None          # (kernel, tokens per tile), asked of the library at the first prompt portion
         self._decode_plans = {}       # (rows, wanted ranges) -> (ranges, as clusters)
         self._ctas_per_sm = None      # CTAs of the decode kernel that an SM holds, asked of the library at the first decode step
@@ -119,6 +124,8 @@ class PagedAttention:
             per_tile = ops.attention_prefill_tc_tokens_per_tile(self.group, self.d)
             if per_tile:
                 self._prefill = (ops.attention_prefill_tc, per_tile)
+            elif self.softcap:
+                self._prefill = (None, 0)           # the mma.sync prompt kernel has no cap: the kernel for every size serves
             else:
                 self._prefill = (ops.attention_prefill, ops.attention_prefill_tokens_per_tile(self.group))
         return self._prefill
@@ -170,7 +177,11 @@ class PagedAttention:
                         more = dict(splits=splits, partial=ctx.runtime.scratch("attn.prefill_partial", words, torch.float32))
                 kernel(q, kv.k_pages, kv.v_pages, ctx.prefill_segments, ctx.n_prefill_segments, tiles, ctx.slots,
                        kv.block_table, out, nq, nkv, d, self.window, self.scale, ctx.error_flag, work_flops=work_flops,
-                       sink=self.sink, **more)
+                       sink=self.sink, **more, **({"softcap": self.softcap} if self.softcap else {}))
+            elif self.softcap:
+                ops.attention_general(q, (nq * d, d), None, None, kv.k_pages, None, kv.v_pages, d, d, ctx.positions, ctx.slots,
+                                      kv.block_table, out, (nq * d, d), ctx.n_tokens, nq, nkv, self.window, self.scale,
+                                      rows=ctx.prefill_rows, error_flag=ctx.error_flag, softcap=self.softcap)
             else:
                 ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out, nq, nkv,
                                       d, self.window, self.scale, rows=ctx.prefill_rows, error_flag=ctx.error_flag)
@@ -180,7 +191,8 @@ class PagedAttention:
         partial, counters = (None, None) if clustered else self._decode_scratch(ctx, n_rows, n_splits)
         ops.attention_decode(q, kv.k_pages, kv.v_pages, rows, ctx.positions, ctx.slots, kv.block_table, out, partial,
                              self.nq, self.nkv, self.d, self.window, self.scale, 0, n_splits, counters,
-                             error_flag=ctx.error_flag, work_bytes=work_bytes, cluster=clustered, all_new=all_new, sink=self.sink)
+                             error_flag=ctx.error_flag, work_bytes=work_bytes, cluster=clustered, all_new=all_new, sink=self.sink,
+                             softcap=self.softcap)
 
     def forward_fused(self, ctx, qkv, kv, out) -> bool:
         """For a step of single decoded tokens and a rotate-half (or no) position encoding: encoding of q and k,

@@ -154,8 +154,9 @@ class SinkAttention(Mixer):
         # kernel for every size
         self.paged = None
         if runtime.compute_dtype == torch.bfloat16 and self.d == self.dv and self.d in ops.DECODE_HEAD_DIMS and \
-                self.nq // self.nkv <= 64 and self.softcap is None:
-            self.paged = PagedAttention(runtime.compute_dtype, self.nq, self.nkv, self.d, self.window, self.scale, sink=self.sink)
+                self.nq // self.nkv <= 64:
+            self.paged = PagedAttention(runtime.compute_dtype, self.nq, self.nkv, self.d, self.window, self.scale, sink=self.sink,
+                                        softcap=self.softcap)
 
     def graph_key(self, ctx) -> tuple:
         return self.paged.graph_key(ctx) if self.paged is not None else ()
