@@ -24,30 +24,52 @@
 namespace {
 constexpr int GLA_THREADS = 256;
 constexpr int GLA_MAX = 256;                  // largest head size of keys and of values
+constexpr int ENCODE_TOKENS = 8;              // tokens a CTA of the encoding kernel serves: a decay weight is read once for all
+
+// 2^x for x <= 0 by the hardware's exponential (relative error about 2^-22, results below the smallest normal number are
+// zero): for the powers inside a chunk, which multiply a term once.  What multiplies the state again and again (a single
+// token's decay, a chunk's whole decay in the carry) takes exp2f, whose error has no side.
+__device__ __forceinline__ float pow2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 template <typename TW>
 __global__ void gla_encode_kernel(float* __restrict__ rows, long long ld, const TW* __restrict__ w_a2,
                                   const float* __restrict__ bias, float* __restrict__ log_decay,
                                   const int* __restrict__ slots, int n_tokens, int heads, int d, int dv, int rank,
                                   float q_scale, float inv_tau) {
-    extern __shared__ float encode_shared[];              // a [rank]
+    extern __shared__ float encode_shared[];              // a [ENCODE_TOKENS][rank]
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x;
-    if (t >= n_tokens || slots[t] < 0) return;
-    float* row = rows + (size_t)t * ld;
-    const float* a = row + (size_t)2 * heads * (d + dv);
-    for (int i = threadIdx.x; i < rank; i += blockDim.x) encode_shared[i] = a[i];
+    const int first = blockIdx.x * ENCODE_TOKENS;
+    const int count = min(ENCODE_TOKENS, n_tokens - first);
+    for (int e = threadIdx.x; e < ENCODE_TOKENS * rank; e += blockDim.x) {
+        const int t = e / rank, r = e - t * rank;
+        encode_shared[e] = t < count ? rows[(size_t)(first + t) * ld + (size_t)2 * heads * (d + dv) + r] : 0.f;
+    }
     __syncthreads();
     const int channels = heads * d;
     for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-        row[c] *= q_scale;
         const TW* w = w_a2 + (size_t)c * rank;
-        float z = bias ? bias[c] : 0.f;
-        for (int r = 0; r < rank; ++r) z = fmaf(to_float(w[r]), encode_shared[r], z);
-        // log(sigmoid(z)) = -softplus(-z) = -(max(-z, 0) + log1p(exp(-|z|)))
-        const float log_sigmoid = -(fmaxf(-z, 0.f) + log1pf(expf(-fabsf(z))));
-        log_decay[(size_t)t * channels + c] = log_sigmoid * inv_tau * 1.4426950408889634f;
+        float z[ENCODE_TOKENS];
+        const float b = bias ? bias[c] : 0.f;
+#pragma unroll
+        for (int t = 0; t < ENCODE_TOKENS; ++t) z[t] = b;
+        for (int r = 0; r < rank; ++r) {                 // (a token's sum runs over r in ascending order whatever else is in the batch)
+            const float wr = to_float(w[r]);
+#pragma unroll
+            for (int t = 0; t < ENCODE_TOKENS; ++t) z[t] = fmaf(wr, encode_shared[t * rank + r], z[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < ENCODE_TOKENS; ++t) {
+            if (t >= count || slots[first + t] < 0) continue;
+            rows[(size_t)(first + t) * ld + c] *= q_scale;
+            // log(sigmoid(z)) = -softplus(-z) = -(max(-z, 0) + log1p(exp(-|z|)))
+            const float log_sigmoid = -(fmaxf(-z[t], 0.f) + log1pf(expf(-fabsf(z[t]))));
+            log_decay[(size_t)(first + t) * channels + c] = log_sigmoid * inv_tau * 1.4426950408889634f;
+        }
     }
 }
 
@@ -132,9 +154,13 @@ gla_single_kernel(const float* __restrict__ rows, long long ld, const float* __r
 __device__ __forceinline__ void running_logs(float* __restrict__ C, int dp, const float* __restrict__ L, long long ld_l,
                                              int len, int d) {
     for (int i = threadIdx.x; i < dp; i += blockDim.x) {
+        float held[CHUNK];                                  // (all of a channel's loads are in flight together)
+#pragma unroll
+        for (int t = 0; t < CHUNK; ++t) held[t] = (t < len && i < d) ? L[(size_t)t * ld_l + i] : 0.f;
         float sum = 0.f;
+#pragma unroll
         for (int t = 0; t < CHUNK; ++t) {
-            if (t < len && i < d) sum += L[(size_t)t * ld_l + i];
+            sum += held[t];
             C[t * dp + i] = sum;
         }
     }
@@ -162,7 +188,7 @@ gla_sums_kernel(const float* __restrict__ rows, long long ld, const float* __res
     __syncthreads();
     for (int e = threadIdx.x; e < len * dp; e += blockDim.x) {
         const int t = e / dp, i = e - t * dp;
-        ks[e] *= exp2f(C[(len - 1) * dp + i] - C[t * dp + i]);
+        ks[e] *= pow2(C[(len - 1) * dp + i] - C[t * dp + i]);
     }
     for (int i = threadIdx.x; i < d; i += blockDim.x) totals[((size_t)blockIdx.x * heads + h) * d + i] = C[(len - 1) * dp + i];
     __syncthreads();
@@ -211,10 +237,21 @@ gla_carry_kernel(const int* __restrict__ segments, int n_segments, const int* __
         float value = S[e];
         float* U = sums + ((size_t)before * heads + h) * size + e;
         const float* total = totals + ((size_t)before * heads + h) * d + i;
-        for (int c = 0; c < chunks; ++c) {
-            const float u = U[(size_t)c * chunk_stride];
-            U[(size_t)c * chunk_stride] = value;
-            value = fmaf(exp2f(total[(size_t)c * heads * d]), value, u);
+        // (a thread walks its element's chunks eight at a time: the loads are in flight together)
+        constexpr int AHEAD = 8;
+        for (int c0 = 0; c0 < chunks; c0 += AHEAD) {
+            float u[AHEAD], a[AHEAD];
+#pragma unroll
+            for (int k = 0; k < AHEAD; ++k) {
+                u[k] = c0 + k < chunks ? U[(size_t)(c0 + k) * chunk_stride] : 0.f;
+                a[k] = c0 + k < chunks ? total[(size_t)(c0 + k) * heads * d] : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < AHEAD; ++k)
+                if (c0 + k < chunks) {
+                    U[(size_t)(c0 + k) * chunk_stride] = value;
+                    value = fmaf(exp2f(a[k]), value, u[k]);
+                }
         }
         S[e] = value;
     }
@@ -251,14 +288,14 @@ gla_output_kernel(const float* __restrict__ rows, long long ld, const float* __r
         float acc = 0.f;
         if (j <= t && t < len) {
             for (int i = lane; i < d; i += 32)
-                acc = fmaf(qs[t * dp + i] * ks[j * dp + i], exp2f(C[t * dp + i] - C[j * dp + i]), acc);
+                acc = fmaf(qs[t * dp + i] * ks[j * dp + i], pow2(C[t * dp + i] - C[j * dp + i]), acc);
             acc = warp_sum(acc);
         }
         if (lane == 0) A[t * CHUNK + j] = acc;
     }
     __syncthreads();
     // the queries take their decay from the chunk's start: q_t * 2^C_t
-    for (int e = threadIdx.x; e < CHUNK * dp; e += blockDim.x) qs[e] *= exp2f(C[e]);
+    for (int e = threadIdx.x; e < CHUNK * dp; e += blockDim.x) qs[e] *= pow2(C[e]);
     __syncthreads();
     // o[t][j] = sum_i (q_t 2^C_t)[i] S_in[i][j] + sum_j' A[t][j'] v_j'[j]: a thread owns four tokens and four columns
     const float* S = sums + ((size_t)blockIdx.x * heads + h) * d * dv;
@@ -266,11 +303,17 @@ gla_output_kernel(const float* __restrict__ rows, long long ld, const float* __r
     for (int tile = threadIdx.x; tile < tiles; tile += blockDim.x) {
         const int t0 = (tile / tiles_j) * 4, j0 = (tile % tiles_j) * 4;
         float acc[4][4] = {};
-#pragma unroll 4
+        const bool aligned = (dv & 3) == 0 && vec;
+#pragma unroll 8
         for (int i = 0; i < d; ++i) {
             float bv[4];
+            if (aligned) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(S + (size_t)i * dv + j0));
+                bv[0] = b.x, bv[1] = b.y, bv[2] = b.z, bv[3] = b.w;
+            } else {
 #pragma unroll
-            for (int y = 0; y < 4; ++y) bv[y] = j0 + y < dv ? __ldg(S + (size_t)i * dv + j0 + y) : 0.f;
+                for (int y = 0; y < 4; ++y) bv[y] = j0 + y < dv ? __ldg(S + (size_t)i * dv + j0 + y) : 0.f;
+            }
 #pragma unroll
             for (int x = 0; x < 4; ++x) {
                 const float a = qs[(t0 + x) * dp + i];
@@ -330,12 +373,13 @@ LIA_EXPORT int lia_gla_encode(float* rows, long long ld, const void* w_a2, int w
     if (heads <= 0 || d <= 0 || dv <= 0 || rank <= 0 || rank > 8192 || !(tau > 0.f) ||
         ld < (long long)2 * heads * (d + dv) + rank)
         return LIA_ERR_SIZE;
-    const size_t bytes = (size_t)rank * sizeof(float);
+    const size_t bytes = (size_t)ENCODE_TOKENS * rank * sizeof(float);
+    const dim3 grid((n_tokens + ENCODE_TOKENS - 1) / ENCODE_TOKENS);
     if (w_dtype == LIA_BF16)
-        return lia_launch(gla_encode_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), bytes, stream, rows, ld,
+        return lia_launch(gla_encode_kernel<__nv_bfloat16>, grid, dim3(256), bytes, stream, rows, ld,
                           (const __nv_bfloat16*)w_a2, bias, log_decay, slots, n_tokens, heads, d, dv, rank, q_scale, 1.0f / tau);
     if (w_dtype == LIA_F32)
-        return lia_launch(gla_encode_kernel<float>, dim3(n_tokens), dim3(256), bytes, stream, rows, ld, (const float*)w_a2,
+        return lia_launch(gla_encode_kernel<float>, grid, dim3(256), bytes, stream, rows, ld, (const float*)w_a2,
                           bias, log_decay, slots, n_tokens, heads, d, dv, rank, q_scale, 1.0f / tau);
     return LIA_ERR_DTYPE;
 }
@@ -358,7 +402,7 @@ LIA_EXPORT int lia_gla(const float* rows, long long ld, const float* log_decay, 
             return LIA_ERR_SIZE;
         float* totals = scratch + (size_t)max_chunks * heads * d * dv;
         const int dp = (d + 3) & ~3, dvp = (dv + 3) & ~3;
-        const int vec = ((d | dv) & 3) == 0 && (ld & 3) == 0 && (((uintptr_t)rows) & 15u) == 0 ? 1 : 0;
+        const int vec = ((d | dv) & 3) == 0 && (ld & 3) == 0 && (((uintptr_t)rows | (uintptr_t)scratch) & 15u) == 0 ? 1 : 0;
         const size_t sums_bytes = (size_t)CHUNK * (2 * dp + dvp) * sizeof(float);
         const size_t out_bytes = gla_output_shared_bytes(d, dv);
         static bool raised = false;

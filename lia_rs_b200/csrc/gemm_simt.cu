@@ -23,7 +23,7 @@ template <typename TA, typename TW, typename TO, int MODE>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw,
                  TO* __restrict__ out, int ldo, int M, int N, int K, float alpha, long long a_batch,
-                 long long w_batch, long long out_batch) {
+                 long long w_batch, long long out_batch, int act) {
     constexpr int NW = (MODE == GEMM_SWIGLU) ? 2 : 1;
     A += (size_t)blockIdx.z * a_batch;                      // one product per blockIdx.z (a single one: all zero)
     W += (size_t)blockIdx.z * w_batch;
@@ -89,7 +89,7 @@ gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, in
                 *dst = from_float<TO>(to_float(*dst) + alpha * acc[0][i][j]);
             } else {
                 const float gate = acc[0][i][j], up = acc[NW - 1][i][j];
-                *dst = from_float<TO>(up * (gate / (1.0f + expf(-gate))));
+                *dst = from_float<TO>(up * (act == 4 ? fmaxf(gate, 0.f) : gate / (1.0f + expf(-gate))));       // act 4: a ReLU gate
             }
         }
     }
@@ -98,13 +98,13 @@ gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, in
 template <typename TA, typename TW, typename TO>
 int launch_modes(int mode, const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M,
                  int N, int K, float alpha, cudaStream_t stream, int batch = 1, long long a_batch = 0,
-                 long long w_batch = 0, long long out_batch = 0) {
+                 long long w_batch = 0, long long out_batch = 0, int act = 0) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
     if (grid.y > 65535 || batch < 1 || batch > 65535) return LIA_ERR_SIZE;
 #define LIA_GEMM(MODE)                                                                          \
     gemm_simt_kernel<TA, TW, TO, MODE><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, \
                                                                  ldw, (TO*)out, ldo, M, N, K, alpha, \
-                                                                 a_batch, w_batch, out_batch)
+                                                                 a_batch, w_batch, out_batch, act)
     if (mode == GEMM_STORE) LIA_GEMM(GEMM_STORE);
     else if (mode == GEMM_ACCUM) LIA_GEMM(GEMM_ACCUM);
     else if (mode == GEMM_SWIGLU) LIA_GEMM(GEMM_SWIGLU);
@@ -120,17 +120,20 @@ int launch_modes(int mode, const void* A, int lda, const void* W, int ldw, void*
 LIA_EXPORT int lia_gemm_simt(int mode, const void* A, int a_dtype, int lda, const void* W, int w_dtype,
                              int ldw, void* out, int out_dtype, int ldo, int M, int N, int K,
                              float alpha, cudaStream_t stream) {
+    const int act = mode >> 8;           // SWIGLU: 4 above the mode's byte makes the gate a ReLU
+    mode &= 0xff;
+    if (act != 0 && !(mode == GEMM_SWIGLU && act == 4)) return LIA_ERR_SIZE;
     if (M <= 0 || N <= 0) return LIA_OK;
     if (K <= 0 || lda < K || ldw < K || ldo < N) return LIA_ERR_SIZE;
     if (mode == GEMM_ACCUM && out_dtype != LIA_F32) return LIA_ERR_DTYPE;
     if (a_dtype == LIA_F32 && w_dtype == LIA_F32 && out_dtype == LIA_F32)
-        return launch_modes<float, float, float>(mode, A, lda, W, ldw, out, ldo, M, N, K, alpha, stream);
+        return launch_modes<float, float, float>(mode, A, lda, W, ldw, out, ldo, M, N, K, alpha, stream, 1, 0, 0, 0, act);
     if (a_dtype == LIA_BF16 && w_dtype == LIA_BF16 && out_dtype == LIA_F32)
         return launch_modes<__nv_bfloat16, __nv_bfloat16, float>(mode, A, lda, W, ldw, out, ldo, M, N, K,
-                                                                 alpha, stream);
+                                                                 alpha, stream, 1, 0, 0, 0, act);
     if (a_dtype == LIA_BF16 && w_dtype == LIA_BF16 && out_dtype == LIA_BF16)
         return launch_modes<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(mode, A, lda, W, ldw, out, ldo, M,
-                                                                         N, K, alpha, stream);
+                                                                         N, K, alpha, stream, 1, 0, 0, 0, act);
     return LIA_ERR_DTYPE;
 }
 

@@ -359,7 +359,7 @@ gemm_stream_kernel(Args a) {
                         up += sums[buf][w][2 * q + 1][token];
                     }
                     if (token < a.M && f < a.N) {
-                        const float value = up * (gate / (1.0f + __expf(-gate)));
+                        const float value = up * (a.activation == 4 ? fmaxf(gate, 0.f) : gate / (1.0f + __expf(-gate)));    // 4: a ReLU gate
                         if (a.out_bf16) reinterpret_cast<__nv_bfloat16*>(a.out)[(size_t)token * a.ldo + f] = __float2bfloat16_rn(value);
                         else reinterpret_cast<float*>(a.out)[(size_t)token * a.ldo + f] = value;
                     }
@@ -731,7 +731,8 @@ LIA_EXPORT int lia_gemm_stream(int mode, const void* X, int ldx, const void* W, 
                                const void* norm_weight, int norm_weight_dtype, float eps, int sms, int stages_cap,
                                int early_stages, int activation, int* error_flag, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return LIA_OK;
-    if (activation < 0 || activation > 4 || (activation && mode != GEMM_STORE)) return LIA_ERR_SIZE;
+    if (activation < 0 || activation > 4 || (activation && mode != GEMM_STORE && !(mode == GEMM_SWIGLU && activation == 4)))
+        return LIA_ERR_SIZE;
     if (M > TOKENS || K <= 0 || K % 64 || ldw % 8 || ldw < K || ldo < N || sms <= 0) return LIA_ERR_SIZE;
     if ((uintptr_t)W & 15u) return LIA_ERR_ALIGN;
     if (norm_src) {

@@ -70,6 +70,7 @@ struct Shape {
     int via_tma;              // 1: the epilogue leaves through shared memory and TMA
     int ldo;
     float alpha;
+    int act;                  // SWIGLU: 0 the gate passes SiLU, 4 ReLU; STORE: 3 the result passes relu(.)^2
     float* partial;           // [splits][M][n_total]
     int* counters;            // [f_tiles * t_tiles], zero between launches
     int* error_flag;
@@ -110,11 +111,16 @@ __device__ __forceinline__ Unit unit_at(const Shape& s, int index) {
     return u;
 }
 
+__device__ __forceinline__ float relu_squared(float z) {
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+}
+
 template <int MODE, typename TO>
-__device__ __forceinline__ void apply_epilogue(TO* dst, float acc, float up, float alpha) {
-    if (MODE == GEMM_STORE) *dst = from_float<TO>(alpha * acc);
+__device__ __forceinline__ void apply_epilogue(TO* dst, float acc, float up, float alpha, int act) {
+    if (MODE == GEMM_STORE) *dst = from_float<TO>(act == 3 ? relu_squared(alpha * acc) : alpha * acc);
     else if (MODE == GEMM_ACCUM) *dst = from_float<TO>(to_float(*dst) + alpha * acc);
-    else *dst = from_float<TO>(up * (acc / (1.0f + __expf(-acc))));
+    else *dst = from_float<TO>(up * (act == 4 ? fmaxf(acc, 0.f) : acc / (1.0f + __expf(-acc))));
 }
 
 template <int MODE, typename TO>
@@ -344,7 +350,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                             for (int c = 0; c < 8; ++c)
                                 if (c0 + c < rows)
-                                    apply_epilogue<MODE, TO>(out + (size_t)(u.t0 + c0 + c) * s.ldo + f, acc[c], up[c], s.alpha);
+                                    apply_epilogue<MODE, TO>(out + (size_t)(u.t0 + c0 + c) * s.ldo + f, acc[c], up[c], s.alpha, s.act);
                         }
                     }
                 }
@@ -367,8 +373,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         float v;
-                        if (MODE == GEMM_SWIGLU) v = up[c] * __fdividef(acc[c], 1.0f + __expf(-acc[c]));
-                        else v = s.alpha * acc[c];
+                        if (MODE == GEMM_SWIGLU) v = up[c] * (s.act == 4 ? fmaxf(acc[c], 0.f) : __fdividef(acc[c], 1.0f + __expf(-acc[c])));
+                        else v = s.act == 3 ? relu_squared(s.alpha * acc[c]) : s.alpha * acc[c];
                         stage[c * TILE_F + group * 32 + lane] = from_float<TO>(v);
                     }
                     fence_async_smem();
@@ -394,7 +400,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         for (int c = 0; c < 16; ++c) {
                             const int t = u.t0 + c0 + c;
                             if (t >= u.t_end) break;
-                            apply_epilogue<MODE, TO>(out + (size_t)t * s.ldo + f, acc[c], up[c], s.alpha);
+                            apply_epilogue<MODE, TO>(out + (size_t)t * s.ldo + f, acc[c], up[c], s.alpha, s.act);
                         }
                     }
                 }
@@ -502,6 +508,9 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, 
 LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int ldw, void* out, int out_dtype,
                            int ldo, int M, int N, int K, float alpha, float* scratch, long long scratch_floats,
                            int sm_count, int* error_flag, cudaStream_t stream) {
+    const int act = mode >> 8;           // the epilogue's variant rides above the mode's byte
+    mode &= 0xff;
+    if (act != 0 && !(mode == GEMM_SWIGLU && act == 4) && !(mode == GEMM_STORE && act == 3)) return LIA_ERR_SIZE;
     if (M <= 0 || N <= 0) return LIA_OK;
     if (K <= 0 || K % 8 || ldx < K || ldw < K || ldo < N || sm_count <= 0) return LIA_ERR_SIZE;
     if (mode != GEMM_STORE && mode != GEMM_ACCUM && mode != GEMM_SWIGLU) return LIA_ERR_SIZE;
@@ -511,6 +520,7 @@ LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int 
     const Plan plan = make_plan(mode, M, N, K, sm_count, scratch ? scratch_floats : 0);
 
     Shape s;
+    s.act = act;
     s.M = M; s.N = N; s.K = K; s.n_total = swiglu ? 2 * N : N;
     s.n_tile = plan.n_tile; s.splits = plan.splits; s.f_tiles = plan.f_tiles; s.t_tiles = plan.t_tiles;
     s.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
@@ -555,6 +565,9 @@ LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int 
 LIA_EXPORT int lia_gemm_tc_grouped(int mode, const void* X, int ldx, int rows_cap, const void* W, int ldw, int groups,
                                    void* out, int out_dtype, int ldo, int N, int K, int n_tile, const int* tiles,
                                    const int* n_tiles, int max_tiles, int sm_count, int* error_flag, cudaStream_t stream) {
+    const int act = mode >> 8;           // the epilogue's variant rides above the mode's byte
+    mode &= 0xff;
+    if (act != 0 && !(mode == GEMM_SWIGLU && act == 4) && !(mode == GEMM_STORE && act == 3)) return LIA_ERR_SIZE;
     if (rows_cap <= 0 || N <= 0 || max_tiles <= 0) return LIA_OK;
     if (K <= 0 || K % 8 || ldx < K || ldw < K || ldo < N || sm_count <= 0 || groups <= 0 || !tiles || !n_tiles) return LIA_ERR_SIZE;
     if (mode != GEMM_STORE && mode != GEMM_SWIGLU) return LIA_ERR_SIZE;
@@ -563,6 +576,7 @@ LIA_EXPORT int lia_gemm_tc_grouped(int mode, const void* X, int ldx, int rows_ca
     if (n_tile < 16 || n_tile > (swiglu ? 128 : 256) || (n_tile & (n_tile - 1)) || (long long)max_tiles * n_tile > rows_cap)
         return LIA_ERR_SIZE;
     Shape s;
+    s.act = act;
     s.M = rows_cap; s.N = N; s.K = K; s.n_total = swiglu ? 2 * N : N;
     s.n_tile = n_tile; s.splits = 1; s.f_tiles = (N + TILE_F - 1) / TILE_F; s.t_tiles = max_tiles;
     s.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
@@ -643,7 +657,7 @@ LIA_EXPORT long long lia_gemm_tc_noalloc_scratch_floats(int mode, int M, int N, 
 LIA_EXPORT int lia_gemm_tc_noalloc(int mode, const void* X, int ldx, const void* W, int ldw, void* out,
                                    int out_dtype, int ldo, int M, int N, int K, float alpha, int sm_count,
                                    int* error_flag, cudaStream_t stream) {
-    if (lia_gemm_tc_noalloc_scratch_floats(mode, M, N, K, sm_count) > NOALLOC_FLOATS) return LIA_ERR_SCRATCH;
+    if (lia_gemm_tc_noalloc_scratch_floats(mode & 0xff, M, N, K, sm_count) > NOALLOC_FLOATS) return LIA_ERR_SCRATCH;
     float* scratch = nullptr;
     const int rc = noalloc_scratch_address(&scratch);
     if (rc != LIA_OK) return rc;

@@ -343,7 +343,7 @@ def reset_scratch(device) -> None:
         _scratch[key][:COUNTER_WORDS].zero_()
 
 
-def gemm_simt(mode, a, w, out, alpha: float = 1.0, label=None):
+def gemm_simt(mode, a, w, out, alpha: float = 1.0, label=None, act: int = 0):
     """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T on the 32-bit pipes; see csrc/gemm_simt.cu."""
     _cuda(a, w, out)
     M, K = a.shape
@@ -352,7 +352,7 @@ def gemm_simt(mode, a, w, out, alpha: float = 1.0, label=None):
     if w.shape[1] != K or out.shape[0] != M or rows_w != (2 * N if mode == GEMM_SWIGLU else N):
         raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     with _timed("gemm_simt", label, work=lambda: _gemm_work(a, w, out)):
-        _check(lib().lia_gemm_simt(mode, _p(a), dtype_code(a.dtype), a.stride(0), _p(w), dtype_code(w.dtype),
+        _check(lib().lia_gemm_simt(mode | (int(act) << 8), _p(a), dtype_code(a.dtype), a.stride(0), _p(w), dtype_code(w.dtype),
                                    w.stride(0), _p(out), dtype_code(out.dtype), out.stride(0), M, N, K, alpha,
                                    _stream()), "gemm_simt")
 
@@ -390,16 +390,17 @@ def gemm_tc_tiles_fill_the_sms(a, out) -> bool:
     return 4 * ((out.shape[1] + 127) // 128) >= 3 * sms
 
 
-def gemm_tc(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None):
+def gemm_tc(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None, act: int = 0):
     """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T on the tensor cores; see csrc/gemm_tc.cu.  Products
-    with few tiles split K and use this device's scratch, so calls on one device must not overlap."""
+    with few tiles split K and use this device's scratch, so calls on one device must not overlap.
+    `act`: with GEMM_SWIGLU, ACT_RELU makes the gate a ReLU; with GEMM_STORE, ACT_RELU_SQUARED squares the result's ReLU."""
     M, K = a.shape
     N = out.shape[1]
     if w.shape[1] != K or out.shape[0] != M or w.shape[0] != (2 * N if mode == GEMM_SWIGLU else N):
         raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     scratch, sms = _device_scratch(a.device)
     with _timed("gemm_tc", label, work=lambda: _gemm_work(a, w, out)):
-        _check(lib().lia_gemm_tc(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
+        _check(lib().lia_gemm_tc(mode | (int(act) << 8), _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
                                  out.stride(0), M, N, K, alpha, _p(scratch), scratch.numel(), sms, _p(error_flag),
                                  _stream()), "gemm_tc")
 
@@ -413,7 +414,7 @@ def gemm_cluster_accepts(mode, a, w, out) -> bool:
     return lib().lia_gemm_cluster_splits(mode, a.shape[0], out.shape[1], a.shape[1], sms) >= 2
 
 
-def gemm_cluster(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None):
+def gemm_cluster(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None, act: int = 0):
     """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T on the tensor cores with K cut over the CTAs of a
     thread-block cluster, partial sums meeting in distributed shared memory; see csrc/gemm_cluster.cu."""
     M, K = a.shape
@@ -422,7 +423,7 @@ def gemm_cluster(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=Non
         raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     _, sms = _device_scratch(a.device)
     with _timed("gemm_cluster", label, work=lambda: _gemm_work(a, w, out)):
-        _check(lib().lia_gemm_cluster(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
+        _check(lib().lia_gemm_cluster(mode | (int(act) << 8), _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
                                       out.stride(0), M, N, K, alpha, sms, _p(error_flag), _stream()), "gemm_cluster")
 
 
@@ -439,7 +440,7 @@ def gemm_skinny_accepts(mode, a, w, out) -> bool:
             and a.stride(1) == 1 and w.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_skinny(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None):
+def gemm_skinny(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None, act: int = 0):
     """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T for M <= 32 tokens: each CTA streams 16 rows of w over
     the whole of K; see csrc/gemm_skinny.cu."""
     M, K = a.shape
@@ -447,7 +448,7 @@ def gemm_skinny(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None
     if w.shape[1] != K or out.shape[0] != M or w.shape[0] != (2 * N if mode == GEMM_SWIGLU else N):
         raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     with _timed("gemm_skinny", label, work=lambda: _gemm_work(a, w, out)):
-        _check(lib().lia_gemm_skinny(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
+        _check(lib().lia_gemm_skinny(mode | (int(act) << 8), _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
                                      out.stride(0), M, N, K, alpha, _p(error_flag), _stream()), "gemm_skinny")
 
 
@@ -476,7 +477,8 @@ def gemm_stream(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None
     """out[M, N] (op)= alpha * x[M, K] @ w[N, K]^T for M <= 16 tokens, one persistent CTA per SM with the
     tokens' rows resident in shared memory; see csrc/gemm_stream.cu.  Without `norm_weight`, x = a (bfloat16);
     with it, a is 32-bit and x = RMSNorm(a; norm_weight, eps) rounded to bfloat16, computed inside the kernel.
-    `activation` (STORE only; ACT_GELU_TANH or ACT_SILU): applied to the 32-bit result before it is stored."""
+    `activation` (STORE: ACT_GELU_TANH, ACT_SILU, ACT_RELU_SQUARED or ACT_RELU, applied to the 32-bit result before it is
+    stored; SWIGLU: ACT_RELU makes the gate a ReLU)."""
     M, K = a.shape
     N = out.shape[1]
     if w.shape[1] != K or out.shape[0] != M or w.shape[0] != (2 * N if mode == GEMM_SWIGLU else N):
@@ -1259,7 +1261,8 @@ def moe_gemm(gated, a, order, top: int, w, out, tiles, n_tiles, max_tiles: int, 
                                   _p(out), out.stride(0), _p(tiles), _p(n_tiles), int(max_tiles), N, K, _stream()), "moe_gemm")
 
 
-def gemm_tc_grouped(mode, a, w, out, tile_rows: int, tiles, n_tiles, max_tiles: int, pairs: int, error_flag=None, label=None):
+def gemm_tc_grouped(mode, a, w, out, tile_rows: int, tiles, n_tiles, max_tiles: int, pairs: int, error_flag=None, label=None,
+                    act: int = 0):
     """out[r] = a[r] @ w[e(r)]^T on the tensor cores, rows sorted and padded by expert as `moe_plan(pad=True)` lists them:
     a [rows, K] bfloat16, w [experts, N or 2 N, K] bfloat16, out [rows, N]; GEMM_STORE or GEMM_SWIGLU (csrc/gemm_tc.cu).
     `pairs`: the rows that belong to a pair (for the profile's count of the work)."""
@@ -1271,7 +1274,7 @@ def gemm_tc_grouped(mode, a, w, out, tile_rows: int, tiles, n_tiles, max_tiles: 
         raise KernelError("gemm_tc_grouped: shapes do not agree")
     _, sms = _device_scratch(a.device)
     with _timed("gemm_tc_grouped", label, nbytes=w.numel() * w.element_size(), flops=2 * pairs * w.shape[1] * K):
-        _check(lib().lia_gemm_tc_grouped(mode, _p(a), a.stride(0), rows, _p(w), K, w.shape[0], _p(out), dtype_code(out.dtype),
+        _check(lib().lia_gemm_tc_grouped(mode | (int(act) << 8), _p(a), a.stride(0), rows, _p(w), K, w.shape[0], _p(out), dtype_code(out.dtype),
                                          out.stride(0), N, K, int(tile_rows), _p(tiles), _p(n_tiles), int(max_tiles), sms,
                                          _p(error_flag), _stream()), "gemm_tc_grouped")
 

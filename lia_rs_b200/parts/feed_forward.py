@@ -3,9 +3,8 @@
 against [Wg; Wu] whose epilogue applies the activation (the reference's gated kernel does the
 same with two matrices: src/gpu/kernels/llama_gated.rs:181-222); the down product adds into the
 residual stream.  Parameters: hidden, intermediate, and optionally `names`: the checkpoint names of the gate, up
-and down matrices behind the part's prefix, and `gate_activation`: "silu" (default) or "relu", act = up * relu(gate); the
-latter takes gate and up as 32-bit rows of the one product and applies the activation in a kernel of its own
-(csrc/norm_residual.cu)."""
+and down matrices behind the part's prefix, and `gate_activation`: "silu" (default) or "relu", act = up * relu(gate), in
+the same epilogues."""
 from __future__ import annotations
 
 import torch
@@ -53,12 +52,8 @@ class SwiGLU(FeedForward):
     def forward(self, ctx, x, residual, scale, store=False):
         rt, n = self.runtime, x.shape[0]
         act = ctx.buffer("ffn.act", (n, self.intermediate), rt.compute_dtype)
-        if self.relu:
-            both = ctx.buffer("ffn.gate_up", (n, 2 * self.intermediate), torch.float32)
-            linear(rt, STORE, x, self.w_gate_up, both, error_flag=ctx.error_flag, name="gate_up")
-            rt.ops.activation_rows(both, act, rt.ops.ACT_RELU, gated=True)
-        else:
-            linear(rt, SWIGLU, x, self.w_gate_up, act, error_flag=ctx.error_flag, name="gate_up")
+        linear(rt, SWIGLU, x, self.w_gate_up, act, error_flag=ctx.error_flag, name="gate_up",
+               gate_activation=rt.ops.ACT_RELU if self.relu else 0)
         linear(rt, STORE if store else ACCUM, act, self.w_down, residual, scale, error_flag=ctx.error_flag, name="down")
 
 

@@ -58,14 +58,19 @@ def _choose(mode, a, w, out) -> int:
 
 
 def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0,
-           error_flag=None, name=None, activation: int = 0, unactivated: torch.Tensor = None):
+           error_flag=None, name=None, activation: int = 0, unactivated: torch.Tensor = None, gate_activation: int = 0):
     """`name`: what the product is to its caller ("qkv", "down", ...), for the per-kernel-class profile.
     `error_flag` (int32[1] on the device, a step's `ctx.error_flag`): a tensor-core kernel that gives up on one
     of its bounded waits raises it to 3, and the step's caller then learns that the result is not to be used.
     `activation` (STORE only; `ops.ACT_GELU_TANH`, `ops.ACT_SILU`): out = act(alpha a w^T).  The few-token persistent
     kernel applies it in its epilogue and the call returns True; where another kernel serves the product, the plain
     product goes to `unactivated` (32-bit rows of out's shape) instead of `out`, the call returns False and the
-    activation is the caller's (`ops.activation_rows`): nothing is rounded ahead of the activation either way."""
+    activation is the caller's (`ops.activation_rows`): nothing is rounded ahead of the activation either way (the squared
+    ReLU is also applied by the persistent tcgen05 kernel).
+    `gate_activation` (SWIGLU only; `ops.ACT_RELU`): out = up * relu(gate) instead of up * silu(gate), in every kernel's
+    epilogue."""
+    if gate_activation and (mode != SWIGLU or gate_activation != ops.ACT_RELU):
+        raise ValueError("a gate activation rides on a SWIGLU product and is ACT_RELU")
     if activation and (mode != STORE or unactivated is None):
         raise ValueError("an activation rides on a STORE product and needs 32-bit rows for the kernels that cannot apply it")
     if isinstance(a, DeferredNorm):
@@ -82,11 +87,11 @@ def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
                                          and ops.gemm_stream_accepts(mode, source, w, out, norm=True))
             if fused:
                 ops.gemm_stream(mode, source, w, out, alpha, error_flag, label=name, norm_weight=norm_weight, eps=eps,
-                                activation=activation)
+                                activation=activation or gate_activation)
                 return bool(activation)
         a = a.tensor()
     if a.dtype != torch.bfloat16:
-        ops.gemm_simt(mode, a, w, unactivated if activation else out, alpha, label=name)
+        ops.gemm_simt(mode, a, w, unactivated if activation else out, alpha, label=name, act=gate_activation)
         return False
     # everything the kernels' acceptance looks at: sizes, row strides, element types, 16-byte alignment of the bases
     key = (mode, a.shape, a.stride(), a.data_ptr() & 15, w.shape, w.stride(), w.dtype, w.data_ptr() & 15,
@@ -98,15 +103,18 @@ def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
         if choice == _STREAM:
             ops.gemm_stream(mode, a, w, out, alpha, error_flag, label=name, activation=activation)
             return True
+        if choice == _TC and activation == ops.ACT_RELU_SQUARED:
+            ops.gemm_tc(mode, a, w, out, alpha, error_flag, label=name, act=activation)
+            return True
         linear(runtime, mode, a, w, unactivated, alpha, error_flag=error_flag, name=name)
         return False
     if choice == _TC:
-        ops.gemm_tc(mode, a, w, out, alpha, error_flag, label=name)
+        ops.gemm_tc(mode, a, w, out, alpha, error_flag, label=name, act=gate_activation)
     elif choice == _STREAM:
-        ops.gemm_stream(mode, a, w, out, alpha, error_flag, label=name)
+        ops.gemm_stream(mode, a, w, out, alpha, error_flag, label=name, activation=gate_activation)
     elif choice == _SKINNY:
-        ops.gemm_skinny(mode, a, w, out, alpha, error_flag, label=name)
+        ops.gemm_skinny(mode, a, w, out, alpha, error_flag, label=name, act=gate_activation)
     elif choice == _CLUSTER:
-        ops.gemm_cluster(mode, a, w, out, alpha, error_flag, label=name)
+        ops.gemm_cluster(mode, a, w, out, alpha, error_flag, label=name, act=gate_activation)
     else:
-        ops.gemm_simt(mode, a, w, out, alpha, label=name)
+        ops.gemm_simt(mode, a, w, out, alpha, label=name, act=gate_activation)

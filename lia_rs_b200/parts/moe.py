@@ -154,10 +154,8 @@ class ExpertMixture(FeedForward):
                 ops.gemm_tc_grouped(SWIGLU, sorted_x, self.w_gate_up, act, tile_rows, tiles, n_tiles, max_tiles, pairs,
                                     error_flag=ctx.error_flag, label="gate_up")
             else:
-                up = scratch("moe.up", rows * self.ff, torch.float32).view(rows, self.ff)
-                ops.gemm_tc_grouped(STORE, sorted_x, self.w_gate_up, up, tile_rows, tiles, n_tiles, max_tiles, pairs,
-                                    error_flag=ctx.error_flag, label="up")
-                ops.activation_rows(up, act, ops.ACT_RELU_SQUARED)
+                ops.gemm_tc_grouped(STORE, sorted_x, self.w_gate_up, act, tile_rows, tiles, n_tiles, max_tiles, pairs,
+                                    error_flag=ctx.error_flag, label="up", act=ops.ACT_RELU_SQUARED)
             ops.gemm_tc_grouped(STORE, act, self.w_down, y, tile_rows, tiles, n_tiles, max_tiles, pairs,
                                 error_flag=ctx.error_flag, label="down")
         else:
