@@ -24,7 +24,6 @@
 namespace {
 constexpr int GLA_THREADS = 256;
 constexpr int GLA_MAX = 256;                  // largest head size of keys and of values
-constexpr int ENCODE_TOKENS = 8;              // tokens a CTA of the encoding kernel serves: a decay weight is read once for all
 
 // 2^x for x <= 0 by the hardware's exponential (relative error about 2^-22, results below the smallest normal number are
 // zero): for the powers inside a chunk, which multiply a term once.  What multiplies the state again and again (a single
@@ -35,7 +34,8 @@ __device__ __forceinline__ float pow2(float x) {
     return y;
 }
 
-template <typename TW>
+// ENCODE_TOKENS tokens a CTA: a decay weight is read once for all of them (prompt portions); 1 for a few single tokens
+template <typename TW, int ENCODE_TOKENS>
 __global__ void gla_encode_kernel(float* __restrict__ rows, long long ld, const TW* __restrict__ w_a2,
                                   const float* __restrict__ bias, float* __restrict__ log_decay,
                                   const int* __restrict__ slots, int n_tokens, int heads, int d, int dv, int rank,
@@ -149,19 +149,22 @@ gla_single_kernel(const float* __restrict__ rows, long long ld, const float* __r
     }
 }
 
-// C [CHUNK][dp]: the running sums of a chunk's log2 decays, C_t = L_0 + ... + L_t per channel (rows behind `len` repeat
+// C [CHUNK][stride]: the running sums of a chunk's log2 decays, C_t = L_0 + ... + L_t per channel (rows behind `len` repeat
 // the last one); a thread a channel
-__device__ __forceinline__ void running_logs(float* __restrict__ C, int dp, const float* __restrict__ L, long long ld_l,
-                                             int len, int d) {
-    for (int i = threadIdx.x; i < dp; i += blockDim.x) {
-        float held[CHUNK];                                  // (all of a channel's loads are in flight together)
-#pragma unroll
-        for (int t = 0; t < CHUNK; ++t) held[t] = (t < len && i < d) ? L[(size_t)t * ld_l + i] : 0.f;
+__device__ __forceinline__ void running_logs(float* __restrict__ C, int stride, int dp, const float* __restrict__ L,
+                                             long long ld_l, int len, int d) {
+    for (int i = threadIdx.x; i < stride; i += blockDim.x) {
         float sum = 0.f;
+        constexpr int AHEAD = 8;                            // (eight of a channel's loads are in flight together)
+        for (int t0 = 0; t0 < CHUNK; t0 += AHEAD) {
+            float held[AHEAD];
 #pragma unroll
-        for (int t = 0; t < CHUNK; ++t) {
-            sum += held[t];
-            C[t * dp + i] = sum;
+            for (int k = 0; k < AHEAD; ++k) held[k] = (t0 + k < len && i < d) ? L[(size_t)(t0 + k) * ld_l + i] : 0.f;
+#pragma unroll
+            for (int k = 0; k < AHEAD; ++k) {
+                sum += held[k];
+                C[(t0 + k) * stride + i] = sum;
+            }
         }
     }
 }
@@ -184,7 +187,7 @@ gla_sums_kernel(const float* __restrict__ rows, long long ld, const float* __res
     const float* chunk_rows = rows + (size_t)first * ld;
     load_chunk(ks, dp, chunk_rows + (size_t)(heads + h) * d, ld, len, d, vec, false, 0.f);
     load_chunk(vs, dvp, chunk_rows + (size_t)2 * heads * d + (size_t)h * dv, ld, len, dv, vec, false, 0.f);
-    running_logs(C, dp, log_decay + (size_t)first * heads * d + (size_t)h * d, (long long)heads * d, len, d);
+    running_logs(C, dp, dp, log_decay + (size_t)first * heads * d + (size_t)h * d, (long long)heads * d, len, d);
     __syncthreads();
     for (int e = threadIdx.x; e < len * dp; e += blockDim.x) {
         const int t = e / dp, i = e - t * dp;
@@ -258,44 +261,55 @@ gla_carry_kernel(const int* __restrict__ segments, int n_segments, const int* __
 }
 
 template <typename TO>
-__global__ void __launch_bounds__(GLA_THREADS)
+__global__ void __launch_bounds__(GLA_THREADS, 3)
 gla_output_kernel(const float* __restrict__ rows, long long ld, const float* __restrict__ log_decay,
                   const int* __restrict__ segments, int n_segments, const float* __restrict__ sums,
                   const float* __restrict__ norm_weight, TO* __restrict__ out, int heads, int d, int dv, float eps, int vec) {
-    extern __shared__ float out_shared[];  // q [CHUNK][dp], k [CHUNK][dp], v [CHUNK][dvp], C [CHUNK][dp], A [CHUNK][CHUNK], o [CHUNK][dvp]
+    // q [CHUNK][ds], k [CHUNK][ds], C [CHUNK][ds], v [CHUNK][dvp], A [CHUNK][CHUNK], o [CHUNK][dvp]; ds = dp + 4: rows four
+    // floats apart from a multiple of 32, so that 32 lanes reading four floats each of 32 different rows meet no bank twice
+    extern __shared__ float out_shared[];
     pdl_launch_dependents();
     pdl_wait();
     int first, len, segment, chunk;
     if (!find_chunk(segments, n_segments, blockIdx.x, &first, &len, &segment, &chunk)) return;
     const int h = blockIdx.y;
-    const int dp = (d + 3) & ~3, dvp = (dv + 3) & ~3;
+    const int dp = (d + 3) & ~3, dvp = (dv + 3) & ~3, ds = dp + 4;
     float* qs = out_shared;
-    float* ks = qs + CHUNK * dp;
-    float* vs = ks + CHUNK * dp;
-    float* C = vs + CHUNK * dvp;
-    float* A = C + CHUNK * dp;
-    float* os = A + CHUNK * CHUNK;
+    float* ks = qs + CHUNK * ds;
+    float* C = ks + CHUNK * ds;
+    float* vs = C + CHUNK * ds;
+    float* A = vs + CHUNK * dvp;
+    // (the outputs take the keys' room where they fit: the keys are done with once A is made)
+    float* os = dvp <= ds ? ks : A + CHUNK * CHUNK;
     const float* chunk_rows = rows + (size_t)first * ld;
-    load_chunk(qs, dp, chunk_rows + (size_t)h * d, ld, len, d, vec, false, 0.f);
-    load_chunk(ks, dp, chunk_rows + (size_t)(heads + h) * d, ld, len, d, vec, false, 0.f);
+    load_chunk(qs, ds, chunk_rows + (size_t)h * d, ld, len, d, vec, false, 0.f);
+    load_chunk(ks, ds, chunk_rows + (size_t)(heads + h) * d, ld, len, d, vec, false, 0.f);
     load_chunk(vs, dvp, chunk_rows + (size_t)2 * heads * d + (size_t)h * dv, ld, len, dv, vec, false, 0.f);
-    running_logs(C, dp, log_decay + (size_t)first * heads * d + (size_t)h * d, (long long)heads * d, len, d);
+    running_logs(C, ds, dp, log_decay + (size_t)first * heads * d + (size_t)h * d, (long long)heads * d, len, d);
     __syncthreads();
-    // A[t][j] = sum_i q_t[i] k_j[i] 2^(C_t[i] - C_j[i]) for j <= t: a warp a pair, its lanes over the channels
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int pair = warp; pair < CHUNK * CHUNK; pair += GLA_THREADS / 32) {
-        const int t = pair / CHUNK, j = pair - t * CHUNK;
+    // A[t][j] = sum_i q_t[i] k_j[i] 2^(C_t[i] - C_j[i]) for j <= t: a thread a pair, a warp one key j and 32 queries t
+    // (the key's row is read by all lanes at once, the queries' rows are `ds` apart), four channels at a time
+    for (int e = threadIdx.x; e < CHUNK * CHUNK; e += blockDim.x) {
+        const int j = e / CHUNK, t = e - j * CHUNK;
         float acc = 0.f;
         if (j <= t && t < len) {
-            for (int i = lane; i < d; i += 32)
-                acc = fmaf(qs[t * dp + i] * ks[j * dp + i], pow2(C[t * dp + i] - C[j * dp + i]), acc);
-            acc = warp_sum(acc);
+            const float4* q4 = reinterpret_cast<const float4*>(qs + t * ds);
+            const float4* ct4 = reinterpret_cast<const float4*>(C + t * ds);
+            const float4* k4 = reinterpret_cast<const float4*>(ks + j * ds);
+            const float4* cj4 = reinterpret_cast<const float4*>(C + j * ds);
+            for (int i = 0; i < dp / 4; ++i) {
+                const float4 q = q4[i], ct = ct4[i], k = k4[i], cj = cj4[i];
+                acc = fmaf(q.x * k.x, pow2(ct.x - cj.x), acc);
+                acc = fmaf(q.y * k.y, pow2(ct.y - cj.y), acc);
+                acc = fmaf(q.z * k.z, pow2(ct.z - cj.z), acc);
+                acc = fmaf(q.w * k.w, pow2(ct.w - cj.w), acc);
+            }
         }
-        if (lane == 0) A[t * CHUNK + j] = acc;
+        A[t * CHUNK + j] = acc;
     }
     __syncthreads();
     // the queries take their decay from the chunk's start: q_t * 2^C_t
-    for (int e = threadIdx.x; e < CHUNK * dp; e += blockDim.x) qs[e] *= pow2(C[e]);
+    for (int e = threadIdx.x; e < CHUNK * ds; e += blockDim.x) qs[e] *= pow2(C[e]);
     __syncthreads();
     // o[t][j] = sum_i (q_t 2^C_t)[i] S_in[i][j] + sum_j' A[t][j'] v_j'[j]: a thread owns four tokens and four columns
     const float* S = sums + ((size_t)blockIdx.x * heads + h) * d * dv;
@@ -316,7 +330,7 @@ gla_output_kernel(const float* __restrict__ rows, long long ld, const float* __r
             }
 #pragma unroll
             for (int x = 0; x < 4; ++x) {
-                const float a = qs[(t0 + x) * dp + i];
+                const float a = qs[(t0 + x) * ds + i];
 #pragma unroll
                 for (int y = 0; y < 4; ++y) acc[x][y] = fmaf(a, bv[y], acc[x][y]);
             }
@@ -338,6 +352,7 @@ gla_output_kernel(const float* __restrict__ rows, long long ld, const float* __r
     }
     __syncthreads();
     // the head's norm over its dv elements, its weight and the gate: a warp a token
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int t = warp; t < len; t += GLA_THREADS / 32) {
         float sum = 0.f;
         for (int j = lane; j < dv; j += 32) sum = fmaf(os[t * dvp + j], os[t * dvp + j], sum);
@@ -354,7 +369,7 @@ gla_output_kernel(const float* __restrict__ rows, long long ld, const float* __r
 
 size_t gla_output_shared_bytes(int d, int dv) {
     const int dp = (d + 3) & ~3, dvp = (dv + 3) & ~3;
-    return ((size_t)3 * CHUNK * dp + (size_t)2 * CHUNK * dvp + CHUNK * CHUNK) * sizeof(float);
+    return ((size_t)3 * CHUNK * (dp + 4) + (size_t)(dvp <= dp + 4 ? 1 : 2) * CHUNK * dvp + CHUNK * CHUNK) * sizeof(float);
 }
 }  // namespace
 
@@ -373,14 +388,21 @@ LIA_EXPORT int lia_gla_encode(float* rows, long long ld, const void* w_a2, int w
     if (heads <= 0 || d <= 0 || dv <= 0 || rank <= 0 || rank > 8192 || !(tau > 0.f) ||
         ld < (long long)2 * heads * (d + dv) + rank)
         return LIA_ERR_SIZE;
-    const size_t bytes = (size_t)ENCODE_TOKENS * rank * sizeof(float);
-    const dim3 grid((n_tokens + ENCODE_TOKENS - 1) / ENCODE_TOKENS);
-    if (w_dtype == LIA_BF16)
-        return lia_launch(gla_encode_kernel<__nv_bfloat16>, grid, dim3(256), bytes, stream, rows, ld,
-                          (const __nv_bfloat16*)w_a2, bias, log_decay, slots, n_tokens, heads, d, dv, rank, q_scale, 1.0f / tau);
-    if (w_dtype == LIA_F32)
-        return lia_launch(gla_encode_kernel<float>, grid, dim3(256), bytes, stream, rows, ld, (const float*)w_a2,
-                          bias, log_decay, slots, n_tokens, heads, d, dv, rank, q_scale, 1.0f / tau);
+    const int per_cta = n_tokens >= 1024 ? 8 : 1;
+    const size_t bytes = (size_t)per_cta * rank * sizeof(float);
+    const dim3 grid((n_tokens + per_cta - 1) / per_cta);
+#define LIA_ENCODE(TW, TOKENS)                                                                                     \
+    return lia_launch(gla_encode_kernel<TW, TOKENS>, grid, dim3(256), bytes, stream, rows, ld, (const TW*)w_a2, bias, \
+                      log_decay, slots, n_tokens, heads, d, dv, rank, q_scale, 1.0f / tau)
+    if (w_dtype == LIA_BF16) {
+        if (per_cta == 8) LIA_ENCODE(__nv_bfloat16, 8);
+        LIA_ENCODE(__nv_bfloat16, 1);
+    }
+    if (w_dtype == LIA_F32) {
+        if (per_cta == 8) LIA_ENCODE(float, 8);
+        LIA_ENCODE(float, 1);
+    }
+#undef LIA_ENCODE
     return LIA_ERR_DTYPE;
 }
 
