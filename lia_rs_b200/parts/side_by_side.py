@@ -3,7 +3,7 @@
     mixer(x) = sum_i scale_i * mixer_i(x).
 
 Each member is a registered mixer with its own parameters and checkpoint prefix; every member adds its share into the
-residual stream itself (the mixers' contract is `residual += scale * f(x)`, so the weights ride on the members' last
+residual stream itself (a mixer's `forward` does `residual += scale * f(x)`, so the weights ride on the members' last
 products and no sum is formed anywhere else).  At most one member may ask for a paged cache and at most one for
 per-request state: the layer's cache and state are handed to those.
 
