@@ -130,7 +130,12 @@ def run_mixer(kind, params, weights, h, dtype, steps, state_shape=None, page_siz
 
 LEFT = [dict(heads=4, kv_heads=2, dim=16, vdim=24, scale=0.25, softcap=5.0, mask={"size": 11}, rot={"base": 1000.0, "dims": 8}),
         dict(heads=3, kv_heads=3, dim=24, vdim=8, scale=0.2, softcap=None, mask=None, rot=None),
-        dict(heads=8, kv_heads=1, dim=64, vdim=64, scale=0.125, softcap=30.0, mask={"size": 33}, rot={"base": 1e6, "dims": 64})]
+        dict(heads=8, kv_heads=1, dim=64, vdim=64, scale=0.125, softcap=30.0, mask={"size": 33}, rot={"base": 1e6, "dims": 64}),
+        # three query heads a key head: the split-key kernel takes them, the tcgen05 prompt kernel does not (the kernel for
+        # every size serves the portions); 32 a key head at head size 32: two groups of 16 in the split-key kernel
+        dict(heads=6, kv_heads=2, dim=64, vdim=64, scale=0.125, softcap=8.0, mask={"size": 20}, rot={"base": 1e4, "dims": 32}),
+        dict(heads=32, kv_heads=1, dim=32, vdim=32, scale=0.18, softcap=15.0, mask={"size": 50}, rot={"base": 1e4, "dims": 32}),
+        dict(heads=4, kv_heads=4, dim=128, vdim=128, scale=0.09, softcap=50.0, mask=None, rot={"base": 5e5, "dims": 64})]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
