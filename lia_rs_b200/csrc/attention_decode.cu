@@ -161,8 +161,9 @@ __device__ __forceinline__ void cluster_merge(const Params& p, uint8_t* smem, in
     cluster_sync_all();                               // nobody leaves while a neighbour may still read its shared memory
 }
 
-// NH: groups of 8 query heads per kv head that the CTA serves (1 or 2)
-template <int D, int NH>
+// NH: groups of 8 query heads per kv head that the CTA serves (1 or 2); CAP: the scores pass a tanh cap (an instantiation
+// of its own, so that the kernel without a cap is what it was)
+template <int D, int NH, bool CAP = false>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(Params p) {
     using T = Tile<D>;
@@ -432,7 +433,7 @@ attention_decode_kernel(Params p) {
             for (int h = 0; h < NH; ++h) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) st[h][i] += st_odd[h][i];
-                if (p.cap_in != 0.f) {
+                if (CAP) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) st[h][i] = tanh_approx(st[h][i] * p.cap_in);
                 }
@@ -702,13 +703,13 @@ size_t decode_smem_bytes() {
     return ring > merge ? (ring > weights ? ring : weights) : (merge > weights ? merge : weights);
 }
 
-template <int D, int NH>
+template <int D, int NH, bool CAP = false>
 int configure_decode() {
     static int state = 0;                  // 1: done, -1: failed
     if (state == 0) {
         state = 1;
-        if (cudaFuncSetAttribute(attention_decode_kernel<D, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem_bytes<D>()) != cudaSuccess ||
-            cudaFuncSetAttribute(attention_decode_kernel<D, NH>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+        if (cudaFuncSetAttribute(attention_decode_kernel<D, NH, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem_bytes<D>()) != cudaSuccess ||
+            cudaFuncSetAttribute(attention_decode_kernel<D, NH, CAP>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
             cudaGetLastError();
             state = -1;
         }
@@ -745,9 +746,9 @@ int max_active_clusters(int size) {
     return cached[size] > 0 ? cached[size] : 0;
 }
 
-template <int D, int NH>
+template <int D, int NH, bool CAP = false>
 int launch_decode(const Params& p, int n_rows, cudaStream_t stream) {
-    int rc = configure_decode<D, NH>();
+    int rc = configure_decode<D, NH, CAP>();
     if (rc != LIA_OK) return rc;
     const size_t smem = decode_smem_bytes<D>();
     const int group = p.nq / p.nkv;
@@ -768,13 +769,13 @@ int launch_decode(const Params& p, int n_rows, cudaStream_t stream) {
         config.attrs = attributes;
         config.numAttrs = lia_pdl_enabled.load(std::memory_order_relaxed) ? 2 : 1;
         lia_launch_counter.fetch_add(1, std::memory_order_relaxed);
-        if (cudaLaunchKernelEx(&config, attention_decode_kernel<D, NH>, p) != cudaSuccess) {
+        if (cudaLaunchKernelEx(&config, attention_decode_kernel<D, NH, CAP>, p) != cudaSuccess) {
             cudaGetLastError();
             return LIA_ERR_LAUNCH;
         }
         return cudaGetLastError() == cudaSuccess ? LIA_OK : LIA_ERR_LAUNCH;
     }
-    rc = lia_launch(attention_decode_kernel<D, NH>, grid, dim3(WARPS * 32), smem, stream, p);
+    rc = lia_launch(attention_decode_kernel<D, NH, CAP>, grid, dim3(WARPS * 32), smem, stream, p);
     if (rc != LIA_OK) return rc;
     if (p.n_splits > 1 && !p.counters)
         rc = lia_launch(attention_merge_kernel<D>, dim3(n_rows, p.nq), dim3(D < 128 ? D : 128), 0, stream, p);
@@ -885,6 +886,12 @@ LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const vo
         p.scale_log2 = softcap * LOG2E;
     }
     const bool wide = nq / nkv > 8;             // more than 8 query heads per kv head: two groups of 8 per CTA
+    if (p.cap_in != 0.f) {
+        if (d == 128) return wide ? launch_decode<128, 2, true>(p, n_rows, stream) : launch_decode<128, 1, true>(p, n_rows, stream);
+        if (d == 64) return wide ? launch_decode<64, 2, true>(p, n_rows, stream) : launch_decode<64, 1, true>(p, n_rows, stream);
+        if (d == 32) return wide ? launch_decode<32, 2, true>(p, n_rows, stream) : launch_decode<32, 1, true>(p, n_rows, stream);
+        return LIA_ERR_SIZE;
+    }
     if (d == 128) return wide ? launch_decode<128, 2>(p, n_rows, stream) : launch_decode<128, 1>(p, n_rows, stream);
     if (d == 64) return wide ? launch_decode<64, 2>(p, n_rows, stream) : launch_decode<64, 1>(p, n_rows, stream);
     if (d == 32) return wide ? launch_decode<32, 2>(p, n_rows, stream) : launch_decode<32, 1>(p, n_rows, stream);

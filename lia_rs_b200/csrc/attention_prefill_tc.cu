@@ -71,7 +71,8 @@ struct Params {
     int sink;                        // 1: one is added to the softmax's denominator (a key of score 0 without a value)
 };
 
-template <int D>
+// CAP: the scores pass a tanh cap (an instantiation of its own, so that the kernel without a cap is what it was)
+template <int D, bool CAP = false>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -268,7 +269,7 @@ attention_prefill_tc_kernel(Params p) {
             uint32_t raw[HALF];
             tmem_load64_nowait(tmem_s + (uint32_t)((j & 1) * KT + half * HALF) + lane_base, raw);
             tmem_load_wait();
-            if (p.cap_in != 0.f) {
+            if (CAP) {
 #pragma unroll
                 for (int c = 0; c < HALF; ++c) raw[c] = __float_as_uint(tanh_approx(__uint_as_float(raw[c]) * p.cap_in));
             }
@@ -477,16 +478,16 @@ __global__ void __launch_bounds__(128) attention_prefill_merge_kernel(Params p) 
     for (int e = 0; e < E; e += 2) *reinterpret_cast<__nv_bfloat162*>(dst + e) = __floats2bfloat162_rn(acc[e] * inv, acc[e + 1] * inv);
 }
 
-template <int D>
+template <int D, bool CAP = false>
 int launch(const Params& p, int n_tiles, cudaStream_t stream) {
     const size_t smem = (size_t)ROWS * D * 2 + (size_t)STAGES * 2 * KT * D * 2 + 1024;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(attention_prefill_tc_kernel<D, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return LIA_ERR_LAUNCH;
         configured = true;
     }
-    const int rc = lia_launch(attention_prefill_tc_kernel<D>, dim3(n_tiles, p.nkv, p.splits), dim3(THREADS), smem, stream, p);
+    const int rc = lia_launch(attention_prefill_tc_kernel<D, CAP>, dim3(n_tiles, p.nkv, p.splits), dim3(THREADS), smem, stream, p);
     if (rc != LIA_OK || p.splits <= 1) return rc;
     return lia_launch(attention_prefill_merge_kernel<D>, dim3(n_tiles, p.nkv, ROWS / 4), dim3(128), 0, stream, p);
 }
@@ -536,6 +537,7 @@ LIA_EXPORT int lia_attention_prefill_tc(const void* q, const void* k_pages, cons
     p.n_rows_total = (long long)n_tokens * nq;
     p.partial_o = partial;
     p.partial_ms = partial ? partial + (size_t)splits * p.n_rows_total * d : nullptr;
+    if (p.cap_in != 0.f) return d == 128 ? launch<128, true>(p, n_tiles, stream) : launch<64, true>(p, n_tiles, stream);
     if (d == 128) return launch<128>(p, n_tiles, stream);
     return launch<64>(p, n_tiles, stream);
 }

@@ -41,7 +41,6 @@ struct Shape {
     int chains;               // accumulators that take the K steps in turn (1, 2 or 4)
     int ldo, vector_ok;       // vector_ok: rows of out may be stored 4 elements at a time
     float alpha;
-    int act;                  // SWIGLU: 0 the gate passes SiLU, 4 ReLU
     int* error_flag;
 };
 
@@ -65,10 +64,10 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr, uint32_t rank) {
 }
 
 template <int MODE, typename TO>
-__device__ __forceinline__ void finish(TO* dst, float acc, float up, float alpha, int act) {
+__device__ __forceinline__ void finish(TO* dst, float acc, float up, float alpha) {
     if (MODE == GEMM_STORE) *dst = from_float<TO>(alpha * acc);
     else if (MODE == GEMM_ACCUM) *dst = from_float<TO>(to_float(*dst) + alpha * acc);
-    else *dst = from_float<TO>(up * (act == 4 ? fmaxf(acc, 0.f) : acc / (1.0f + __expf(-acc))));
+    else *dst = from_float<TO>(up * (acc / (1.0f + __expf(-acc))));
 }
 
 template <int MODE, typename TO>
@@ -278,7 +277,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 } else {
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
-                        r[i] = MODE == GEMM_SWIGLU ? up[i] * (s.act == 4 ? fmaxf(acc[i], 0.f) : acc[i] / (1.0f + __expf(-acc[i]))) : s.alpha * acc[i];
+                        r[i] = MODE == GEMM_SWIGLU ? up[i] * (acc[i] / (1.0f + __expf(-acc[i]))) : s.alpha * acc[i];
                 }
                 if (sizeof(TO) == 4) {
                     *reinterpret_cast<float4*>(dst) = make_float4(r[0], r[1], r[2], r[3]);
@@ -292,7 +291,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             } else {
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    if (f + i < s.N) finish<MODE, TO>(dst + i, acc[i], up[i], s.alpha, s.act);
+                    if (f + i < s.N) finish<MODE, TO>(dst + i, acc[i], up[i], s.alpha);
             }
         }
     }
@@ -406,9 +405,6 @@ LIA_EXPORT int lia_gemm_cluster_splits(int mode, int M, int N, int K, int sm_cou
 LIA_EXPORT int lia_gemm_cluster(int mode, const void* X, int ldx, const void* W, int ldw, void* out, int out_dtype,
                                 int ldo, int M, int N, int K, float alpha, int sm_count, int* error_flag,
                                 cudaStream_t stream) {
-    const int act = mode >> 8;           // SWIGLU: 4 above the mode's byte makes the gate a ReLU
-    mode &= 0xff;
-    if (act != 0 && !(mode == GEMM_SWIGLU && act == 4)) return LIA_ERR_SIZE;
     if (M <= 0 || N <= 0) return LIA_OK;
     if (K <= 0 || K % 8 || ldx < K || ldw < K || ldo < N || sm_count <= 0) return LIA_ERR_SIZE;
     if (mode != GEMM_STORE && mode != GEMM_ACCUM && mode != GEMM_SWIGLU) return LIA_ERR_SIZE;
@@ -419,7 +415,6 @@ LIA_EXPORT int lia_gemm_cluster(int mode, const void* X, int ldx, const void* W,
     if (plan.splits < 2) return LIA_ERR_SIZE;
 
     Shape s;
-    s.act = act;
     s.M = M; s.N = N; s.K = K;
     s.n_tile = plan.n_tile; s.splits = plan.splits; s.f_tiles = plan.f_tiles; s.t_tiles = plan.t_tiles;
     s.kblocks = (K + BLOCK_K - 1) / BLOCK_K;

@@ -77,7 +77,6 @@ struct Args {
     void* out;
     int ldw, ldx, ldo, M, N, K, stages, chunks;
     float alpha;
-    int act;                  // SWIGLU: 0 the gate passes SiLU, 4 ReLU
     int* error_flag;
 };
 
@@ -223,7 +222,7 @@ gemm_skinny_kernel(Args a) {
                 gate += sums[w][r][token];
                 up += sums[w][r + 8][token];
             }
-            out[(size_t)token * a.ldo + f] = from_float<TO>(up * (a.act == 4 ? fmaxf(gate, 0.f) : gate / (1.0f + __expf(-gate))));
+            out[(size_t)token * a.ldo + f] = from_float<TO>(up * (gate / (1.0f + __expf(-gate))));
         }
     } else {
         for (int i = threadIdx.x; i < ROWS * NT * 8; i += THREADS) {
@@ -280,9 +279,6 @@ LIA_EXPORT int lia_gemm_skinny_max_tokens() { return 32; }
 // pointers that are not 16-byte aligned (bulk copies and 16-byte loads need both).
 LIA_EXPORT int lia_gemm_skinny(int mode, const void* X, int ldx, const void* W, int ldw, void* out, int out_dtype,
                                int ldo, int M, int N, int K, float alpha, int* error_flag, cudaStream_t stream) {
-    const int act = mode >> 8;           // SWIGLU: 4 above the mode's byte makes the gate a ReLU
-    mode &= 0xff;
-    if (act != 0 && !(mode == GEMM_SWIGLU && act == 4)) return LIA_ERR_SIZE;
     if (M <= 0 || N <= 0) return LIA_OK;
     if (M > 32 || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldo < N) return LIA_ERR_SIZE;
     if (((uintptr_t)X & 15u) || ((uintptr_t)W & 15u)) return LIA_ERR_ALIGN;
@@ -292,7 +288,6 @@ LIA_EXPORT int lia_gemm_skinny(int mode, const void* X, int ldx, const void* W, 
     Args a;
     a.W = (const __nv_bfloat16*)W; a.X = (const __nv_bfloat16*)X; a.out = out;
     a.ldw = ldw; a.ldx = ldx; a.ldo = ldo; a.M = M; a.N = N; a.K = K; a.alpha = alpha; a.error_flag = error_flag;
-    a.act = act;
     a.chunks = (K + CHUNK_K - 1) / CHUNK_K;
     const long long blocks = mode == GEMM_SWIGLU ? (N + 7) / 8 : (N + ROWS - 1) / ROWS;
     if (blocks > 2147483647LL) return LIA_ERR_SIZE;

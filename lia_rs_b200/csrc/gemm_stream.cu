@@ -42,6 +42,12 @@
 #define GEMM_STORE 0
 #define GEMM_ACCUM 1
 #define GEMM_SWIGLU 2
+// Two more forms, instantiations of their own so that the three above are what they were: the gated form with a ReLU
+// gate, out = up * relu(gate), and the storing form with out = relu(alpha * sum)^2.
+#define GEMM_REGLU 3
+#define GEMM_STORE_RELU2 4
+#define GATED(MODE) ((MODE) == GEMM_SWIGLU || (MODE) == GEMM_REGLU)
+#define STORES(MODE) ((MODE) == GEMM_STORE || (MODE) == GEMM_STORE_RELU2)
 
 namespace {
 constexpr int ROWS = 16;                 // rows of W per block: the MMA's M
@@ -118,7 +124,7 @@ struct Args {
     int stages, early, chunks, ck;   // ring; stages asked for before the tokens' rows; K chunks per block; elements of K per chunk (a multiple of 64)
     int blocks, x_pitch, stage_bytes, half_bytes;
     int norm, out_bf16;              // norm: 0 none, 1 weight bf16, 2 weight f32
-    int activation;                  // STORE only: 0 none, 1 GELU (tanh form), 2 SiLU, 3 ReLU squared, 4 ReLU, applied to alpha * sum before the store
+    int activation;                  // STORE only: 0 none, 1 GELU (tanh form), 2 SiLU, applied to alpha * sum before the store
     float alpha, eps;
     int* error_flag;
 };
@@ -126,7 +132,7 @@ struct Args {
 // Row of W in half `half` (0, 1), place `i` (0..7) of block `block` (-1: none).
 template <int MODE>
 __device__ __forceinline__ int weight_row(const Args& a, int block, int half, int i) {
-    if (MODE == GEMM_SWIGLU) {
+    if (GATED(MODE)) {
         const int f = block * HALF_ROWS + i;
         return f < a.N ? (half == 0 ? f : a.N + f) : -1;
     }
@@ -336,7 +342,7 @@ gemm_stream_kernel(Args a) {
         int ui = 0;
         for (int block = blockIdx.x; block < a.blocks; block += grid, ++ui) {
             const int buf = ui & 1;
-            constexpr int PER_LANE = (MODE == GEMM_SWIGLU ? HALF_ROWS : ROWS) * NT * 8 / 32;
+            constexpr int PER_LANE = (GATED(MODE) ? HALF_ROWS : ROWS) * NT * 8 / 32;
             float old[PER_LANE];
             if (MODE == GEMM_ACCUM) {
 #pragma unroll
@@ -349,7 +355,7 @@ gemm_stream_kernel(Args a) {
 #pragma unroll
             for (int j = 0; j < PER_LANE; ++j) {
                 const int i = lane + j * 32;
-                if (MODE == GEMM_SWIGLU) {
+                if (GATED(MODE)) {
                     // row 2q of the MMA is gate row q of the block, row 2q + 1 its up row
                     const int token = i >> 3, q = i & 7, f = block * HALF_ROWS + q;
                     float gate = 0.f, up = 0.f;
@@ -359,7 +365,7 @@ gemm_stream_kernel(Args a) {
                         up += sums[buf][w][2 * q + 1][token];
                     }
                     if (token < a.M && f < a.N) {
-                        const float value = up * (a.activation == 4 ? fmaxf(gate, 0.f) : gate / (1.0f + __expf(-gate)));    // 4: a ReLU gate
+                        const float value = up * (MODE == GEMM_REGLU ? fmaxf(gate, 0.f) : gate / (1.0f + __expf(-gate)));
                         if (a.out_bf16) reinterpret_cast<__nv_bfloat16*>(a.out)[(size_t)token * a.ldo + f] = __float2bfloat16_rn(value);
                         else reinterpret_cast<float*>(a.out)[(size_t)token * a.ldo + f] = value;
                     }
@@ -369,16 +375,16 @@ gemm_stream_kernel(Args a) {
 #pragma unroll
                     for (int w = 0; w < MMA_WARPS; ++w) total += sums[buf][w][m][token];
                     if (token < a.M && f < a.N) {
-                        float value = MODE == GEMM_STORE ? a.alpha * total : old[j] + a.alpha * total;
+                        float value = STORES(MODE) ? a.alpha * total : old[j] + a.alpha * total;
                         if (MODE == GEMM_STORE && a.activation == 1) {
                             // 0.5 z (1 + tanh(u)), u = sqrt(2/pi) (z + 0.044715 z^3), as z / (1 + exp(-2u))
                             const float u = 0.7978845608028654f * (value + 0.044715f * value * value * value);
                             value = value / (1.0f + expf(-2.0f * u));
                         } else if (MODE == GEMM_STORE && a.activation == 2) {
                             value = value / (1.0f + expf(-value));
-                        } else if (MODE == GEMM_STORE && a.activation >= 3) {          // 3: relu(z)^2, 4: relu(z)
+                        } else if (MODE == GEMM_STORE_RELU2) {
                             value = fmaxf(value, 0.f);
-                            if (a.activation == 3) value *= value;
+                            value *= value;
                         }
                         if (a.out_bf16) reinterpret_cast<__nv_bfloat16*>(a.out)[(size_t)token * a.ldo + f] = __float2bfloat16_rn(value);
                         else reinterpret_cast<float*>(a.out)[(size_t)token * a.ldo + f] = value;
@@ -725,14 +731,17 @@ LIA_EXPORT int lia_gemm_stream_stages(int mode, int M, int N, int K, int with_no
 // pointers that are not 16-byte aligned (bulk copies and 16-byte loads need both), and sizes whose rows do not
 // fit in shared memory beside a ring (ask lia_gemm_stream_stages first).  `stages_cap` > 0 limits the ring;
 // `early_stages` > 0 sets how many stages the producer asks for before the tokens' rows have been asked for (default 2).
-// `activation` (STORE only): 1 the tanh form of GELU, 2 SiLU, 3 the square of ReLU, 4 ReLU, applied to the 32-bit result before it is stored.
+// `activation`: STORE: 1 the tanh form of GELU, 2 SiLU, 3 the square of ReLU; SWIGLU: 4 makes the gate a ReLU; applied to the 32-bit result before it is stored.
 LIA_EXPORT int lia_gemm_stream(int mode, const void* X, int ldx, const void* W, int ldw, void* out, int out_dtype,
                                int ldo, int M, int N, int K, float alpha, const float* norm_src, int ld_norm,
                                const void* norm_weight, int norm_weight_dtype, float eps, int sms, int stages_cap,
                                int early_stages, int activation, int* error_flag, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return LIA_OK;
-    if (activation < 0 || activation > 4 || (activation && mode != GEMM_STORE && !(mode == GEMM_SWIGLU && activation == 4)))
-        return LIA_ERR_SIZE;
+    // the kernel's form: the mode, or one of the two forms that an activation selects
+    int form = mode;
+    if (mode == GEMM_SWIGLU && activation == 4) form = GEMM_REGLU, activation = 0;
+    else if (mode == GEMM_STORE && activation == 3) form = GEMM_STORE_RELU2, activation = 0;
+    if (activation < 0 || activation > 2 || (activation && mode != GEMM_STORE)) return LIA_ERR_SIZE;
     if (M > TOKENS || K <= 0 || K % 64 || ldw % 8 || ldw < K || ldo < N || sms <= 0) return LIA_ERR_SIZE;
     if ((uintptr_t)W & 15u) return LIA_ERR_ALIGN;
     if (norm_src) {
@@ -766,7 +775,9 @@ LIA_EXPORT int lia_gemm_stream(int mode, const void* X, int ldx, const void* W, 
     if (a.stages <= 0) return LIA_ERR_SIZE;
     if (stages_cap > 0 && a.stages > stages_cap) a.stages = stages_cap;
     a.early = early_stages > 0 ? early_stages : 2;
-    if (mode == GEMM_STORE) return launch_form<GEMM_STORE>(a, form_chunks, form_pw, ctas, stream);
-    if (mode == GEMM_ACCUM) return launch_form<GEMM_ACCUM>(a, form_chunks, form_pw, ctas, stream);
+    if (form == GEMM_STORE) return launch_form<GEMM_STORE>(a, form_chunks, form_pw, ctas, stream);
+    if (form == GEMM_ACCUM) return launch_form<GEMM_ACCUM>(a, form_chunks, form_pw, ctas, stream);
+    if (form == GEMM_REGLU) return launch_form<GEMM_REGLU>(a, form_chunks, form_pw, ctas, stream);
+    if (form == GEMM_STORE_RELU2) return launch_form<GEMM_STORE_RELU2>(a, form_chunks, form_pw, ctas, stream);
     return launch_form<GEMM_SWIGLU>(a, form_chunks, form_pw, ctas, stream);
 }

@@ -47,6 +47,11 @@ using namespace tc5;
 #define GEMM_STORE 0
 #define GEMM_ACCUM 1
 #define GEMM_SWIGLU 2
+// Two more forms of the kernel, instantiations of their own so that the three above are what they were: the gated form
+// with a ReLU gate, out = up * relu(gate), and the storing form with out = relu(alpha * sum)^2.
+#define GEMM_REGLU 3
+#define GEMM_STORE_RELU2 4
+#define GATED(MODE) ((MODE) == GEMM_SWIGLU || (MODE) == GEMM_REGLU)
 
 namespace {
 constexpr int THREADS = 192;
@@ -70,7 +75,6 @@ struct Shape {
     int via_tma;              // 1: the epilogue leaves through shared memory and TMA
     int ldo;
     float alpha;
-    int act;                  // SWIGLU: 0 the gate passes SiLU, 4 ReLU; STORE: 3 the result passes relu(.)^2
     float* partial;           // [splits][M][n_total]
     int* counters;            // [f_tiles * t_tiles], zero between launches
     int* error_flag;
@@ -117,10 +121,12 @@ __device__ __forceinline__ float relu_squared(float z) {
 }
 
 template <int MODE, typename TO>
-__device__ __forceinline__ void apply_epilogue(TO* dst, float acc, float up, float alpha, int act) {
-    if (MODE == GEMM_STORE) *dst = from_float<TO>(act == 3 ? relu_squared(alpha * acc) : alpha * acc);
+__device__ __forceinline__ void apply_epilogue(TO* dst, float acc, float up, float alpha) {
+    if (MODE == GEMM_STORE) *dst = from_float<TO>(alpha * acc);
+    else if (MODE == GEMM_STORE_RELU2) *dst = from_float<TO>(relu_squared(alpha * acc));
+    else if (MODE == GEMM_REGLU) *dst = from_float<TO>(up * fmaxf(acc, 0.f));
     else if (MODE == GEMM_ACCUM) *dst = from_float<TO>(to_float(*dst) + alpha * acc);
-    else *dst = from_float<TO>(up * (act == 4 ? fmaxf(acc, 0.f) : acc / (1.0f + __expf(-acc))));
+    else *dst = from_float<TO>(up * (acc / (1.0f + __expf(-acc))));
 }
 
 template <int MODE, typename TO>
@@ -132,7 +138,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __shared__ uint32_t tmem_base_slot;
     __shared__ int last_flag;
 
-    constexpr int A_TILES = (MODE == GEMM_SWIGLU) ? 2 : 1;
+    constexpr int A_TILES = GATED(MODE) ? 2 : 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t a_bytes = TILE_F * BLOCK_K * 2, b_bytes = (uint32_t)s.n_tile * BLOCK_K * 2;
     const uint32_t stage_bytes = A_TILES * a_bytes + b_bytes;
@@ -295,14 +301,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (u.t0 + c0 >= s.M) break;
                     float acc[16], up[16];
                     tmem_load16(lane_addr + (uint32_t)c0, acc);
-                    if (MODE == GEMM_SWIGLU) tmem_load16(lane_addr + (uint32_t)(s.n_tile + c0), up);
+                    if (GATED(MODE)) tmem_load16(lane_addr + (uint32_t)(s.n_tile + c0), up);
                     if (f < s.N) {
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
                             const int t = u.t0 + c0 + c;
                             if (t >= s.M) break;
                             plane[(size_t)t * s.n_total + f] = acc[c];
-                            if (MODE == GEMM_SWIGLU) plane[(size_t)t * s.n_total + s.N + f] = up[c];
+                            if (GATED(MODE)) plane[(size_t)t * s.n_total + s.N + f] = up[c];
                         }
                     }
                 }
@@ -336,7 +342,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                                     for (int c = 0; c < 8; ++c) {
                                         const bool there = sp0 + j < s.splits && c0 + c < rows;
                                         v[j][c] = there ? __ldcg(src + (size_t)c * s.n_total) : 0.f;
-                                        if (MODE == GEMM_SWIGLU) w[j][c] = there ? __ldcg(src + (size_t)c * s.n_total + s.N) : 0.f;
+                                        if (GATED(MODE)) w[j][c] = there ? __ldcg(src + (size_t)c * s.n_total + s.N) : 0.f;
                                     }
                                 }
 #pragma unroll
@@ -344,13 +350,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                                     for (int c = 0; c < 8; ++c) {
                                         acc[c] += v[j][c];
-                                        if (MODE == GEMM_SWIGLU) up[c] += w[j][c];
+                                        if (GATED(MODE)) up[c] += w[j][c];
                                     }
                             }
 #pragma unroll
                             for (int c = 0; c < 8; ++c)
                                 if (c0 + c < rows)
-                                    apply_epilogue<MODE, TO>(out + (size_t)(u.t0 + c0 + c) * s.ldo + f, acc[c], up[c], s.alpha, s.act);
+                                    apply_epilogue<MODE, TO>(out + (size_t)(u.t0 + c0 + c) * s.ldo + f, acc[c], up[c], s.alpha);
                         }
                     }
                 }
@@ -361,7 +367,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (u.t0 + c0 >= u.t_end) break;
                     float acc[32], up[32];
                     tmem_load32_nowait(lane_addr + (uint32_t)c0, acc);
-                    if (MODE == GEMM_SWIGLU) tmem_load32_nowait(lane_addr + (uint32_t)(s.n_tile + c0), up);
+                    if (GATED(MODE)) tmem_load32_nowait(lane_addr + (uint32_t)(s.n_tile + c0), up);
                     tmem_load_wait();
                     const int sbuf = chunk_count & 1;
                     ++chunk_count;
@@ -373,8 +379,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         float v;
-                        if (MODE == GEMM_SWIGLU) v = up[c] * (s.act == 4 ? fmaxf(acc[c], 0.f) : __fdividef(acc[c], 1.0f + __expf(-acc[c])));
-                        else v = s.act == 3 ? relu_squared(s.alpha * acc[c]) : s.alpha * acc[c];
+                        if (MODE == GEMM_SWIGLU) v = up[c] * __fdividef(acc[c], 1.0f + __expf(-acc[c]));
+                        else if (MODE == GEMM_REGLU) v = up[c] * fmaxf(acc[c], 0.f);
+                        else if (MODE == GEMM_STORE_RELU2) v = relu_squared(s.alpha * acc[c]);
+                        else v = s.alpha * acc[c];
                         stage[c * TILE_F + group * 32 + lane] = from_float<TO>(v);
                     }
                     fence_async_smem();
@@ -394,13 +402,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (u.t0 + c0 >= u.t_end) break;                // uniform over the warp
                     float acc[16], up[16];
                     tmem_load16(lane_addr + (uint32_t)c0, acc);
-                    if (MODE == GEMM_SWIGLU) tmem_load16(lane_addr + (uint32_t)(s.n_tile + c0), up);
+                    if (GATED(MODE)) tmem_load16(lane_addr + (uint32_t)(s.n_tile + c0), up);
                     if (f < s.N) {
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
                             const int t = u.t0 + c0 + c;
                             if (t >= u.t_end) break;
-                            apply_epilogue<MODE, TO>(out + (size_t)t * s.ldo + f, acc[c], up[c], s.alpha, s.act);
+                            apply_epilogue<MODE, TO>(out + (size_t)t * s.ldo + f, acc[c], up[c], s.alpha);
                         }
                     }
                 }
@@ -520,7 +528,6 @@ LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int 
     const Plan plan = make_plan(mode, M, N, K, sm_count, scratch ? scratch_floats : 0);
 
     Shape s;
-    s.act = act;
     s.M = M; s.N = N; s.K = K; s.n_total = swiglu ? 2 * N : N;
     s.n_tile = plan.n_tile; s.splits = plan.splits; s.f_tiles = plan.f_tiles; s.t_tiles = plan.t_tiles;
     s.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
@@ -550,6 +557,14 @@ LIA_EXPORT int lia_gemm_tc(int mode, const void* X, int ldx, const void* W, int 
     }
     const long long units = (long long)plan.f_tiles * plan.t_tiles * plan.splits;
     const int grid = (int)min((long long)sm_count, units);
+    if (mode == GEMM_STORE && act == 3) {
+        if (out_dtype == LIA_F32) return launch<GEMM_STORE_RELU2, float>(mw, mx, mo, (float*)out, s, grid, stream);
+        return launch<GEMM_STORE_RELU2, __nv_bfloat16>(mw, mx, mo, (__nv_bfloat16*)out, s, grid, stream);
+    }
+    if (mode == GEMM_SWIGLU && act == 4) {
+        if (out_dtype == LIA_F32) return launch<GEMM_REGLU, float>(mw, mx, mo, (float*)out, s, grid, stream);
+        return launch<GEMM_REGLU, __nv_bfloat16>(mw, mx, mo, (__nv_bfloat16*)out, s, grid, stream);
+    }
     if (mode == GEMM_STORE && out_dtype == LIA_F32) return launch<GEMM_STORE, float>(mw, mx, mo, (float*)out, s, grid, stream);
     if (mode == GEMM_STORE) return launch<GEMM_STORE, __nv_bfloat16>(mw, mx, mo, (__nv_bfloat16*)out, s, grid, stream);
     if (mode == GEMM_ACCUM) return launch<GEMM_ACCUM, float>(mw, mx, mo, (float*)out, s, grid, stream);
@@ -576,7 +591,6 @@ LIA_EXPORT int lia_gemm_tc_grouped(int mode, const void* X, int ldx, int rows_ca
     if (n_tile < 16 || n_tile > (swiglu ? 128 : 256) || (n_tile & (n_tile - 1)) || (long long)max_tiles * n_tile > rows_cap)
         return LIA_ERR_SIZE;
     Shape s;
-    s.act = act;
     s.M = rows_cap; s.N = N; s.K = K; s.n_total = swiglu ? 2 * N : N;
     s.n_tile = n_tile; s.splits = 1; s.f_tiles = (N + TILE_F - 1) / TILE_F; s.t_tiles = max_tiles;
     s.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
@@ -605,6 +619,14 @@ LIA_EXPORT int lia_gemm_tc_grouped(int mode, const void* X, int ldx, int rows_ca
     }
     const long long units = (long long)s.f_tiles * max_tiles;
     const int grid = (int)min((long long)sm_count, units);
+    if (mode == GEMM_STORE && act == 3) {
+        if (out_dtype == LIA_F32) return launch<GEMM_STORE_RELU2, float>(mw, mx, mo, (float*)out, s, grid, stream);
+        return launch<GEMM_STORE_RELU2, __nv_bfloat16>(mw, mx, mo, (__nv_bfloat16*)out, s, grid, stream);
+    }
+    if (mode == GEMM_SWIGLU && act == 4) {
+        if (out_dtype == LIA_F32) return launch<GEMM_REGLU, float>(mw, mx, mo, (float*)out, s, grid, stream);
+        return launch<GEMM_REGLU, __nv_bfloat16>(mw, mx, mo, (__nv_bfloat16*)out, s, grid, stream);
+    }
     if (mode == GEMM_STORE && out_dtype == LIA_F32) return launch<GEMM_STORE, float>(mw, mx, mo, (float*)out, s, grid, stream);
     if (mode == GEMM_STORE) return launch<GEMM_STORE, __nv_bfloat16>(mw, mx, mo, (__nv_bfloat16*)out, s, grid, stream);
     if (out_dtype == LIA_F32) return launch<GEMM_SWIGLU, float>(mw, mx, mo, (float*)out, s, grid, stream);

@@ -414,7 +414,7 @@ def gemm_cluster_accepts(mode, a, w, out) -> bool:
     return lib().lia_gemm_cluster_splits(mode, a.shape[0], out.shape[1], a.shape[1], sms) >= 2
 
 
-def gemm_cluster(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None, act: int = 0):
+def gemm_cluster(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None):
     """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T on the tensor cores with K cut over the CTAs of a
     thread-block cluster, partial sums meeting in distributed shared memory; see csrc/gemm_cluster.cu."""
     M, K = a.shape
@@ -423,7 +423,7 @@ def gemm_cluster(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=Non
         raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     _, sms = _device_scratch(a.device)
     with _timed("gemm_cluster", label, work=lambda: _gemm_work(a, w, out)):
-        _check(lib().lia_gemm_cluster(mode | (int(act) << 8), _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
+        _check(lib().lia_gemm_cluster(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
                                       out.stride(0), M, N, K, alpha, sms, _p(error_flag), _stream()), "gemm_cluster")
 
 
@@ -440,7 +440,7 @@ def gemm_skinny_accepts(mode, a, w, out) -> bool:
             and a.stride(1) == 1 and w.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_skinny(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None, act: int = 0):
+def gemm_skinny(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None):
     """out[M, N] (op)= alpha * a[M, K] @ w[N, K]^T for M <= 32 tokens: each CTA streams 16 rows of w over
     the whole of K; see csrc/gemm_skinny.cu."""
     M, K = a.shape
@@ -448,7 +448,7 @@ def gemm_skinny(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None
     if w.shape[1] != K or out.shape[0] != M or w.shape[0] != (2 * N if mode == GEMM_SWIGLU else N):
         raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     with _timed("gemm_skinny", label, work=lambda: _gemm_work(a, w, out)):
-        _check(lib().lia_gemm_skinny(mode | (int(act) << 8), _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
+        _check(lib().lia_gemm_skinny(mode, _p(a), a.stride(0), _p(w), w.stride(0), _p(out), dtype_code(out.dtype),
                                      out.stride(0), M, N, K, alpha, _p(error_flag), _stream()), "gemm_skinny")
 
 

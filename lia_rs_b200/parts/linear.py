@@ -67,8 +67,8 @@ def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
     product goes to `unactivated` (32-bit rows of out's shape) instead of `out`, the call returns False and the
     activation is the caller's (`ops.activation_rows`): nothing is rounded ahead of the activation either way (the squared
     ReLU is also applied by the persistent tcgen05 kernel).
-    `gate_activation` (SWIGLU only; `ops.ACT_RELU`): out = up * relu(gate) instead of up * silu(gate), in every kernel's
-    epilogue."""
+    `gate_activation` (SWIGLU only; `ops.ACT_RELU`): out = up * relu(gate) instead of up * silu(gate), in the epilogue of
+    the persistent few-token kernel, of the persistent tcgen05 kernel and of the product on the 32-bit pipes."""
     if gate_activation and (mode != SWIGLU or gate_activation != ops.ACT_RELU):
         raise ValueError("a gate activation rides on a SWIGLU product and is ACT_RELU")
     if activation and (mode != STORE or unactivated is None):
@@ -100,7 +100,7 @@ def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
     if choice is None:
         choice = _choices[key] = _choose(mode, a, w, out)
     if activation:
-        if choice == _STREAM:
+        if choice == _STREAM and activation in (ops.ACT_GELU_TANH, ops.ACT_SILU, ops.ACT_RELU_SQUARED):
             ops.gemm_stream(mode, a, w, out, alpha, error_flag, label=name, activation=activation)
             return True
         if choice == _TC and activation == ops.ACT_RELU_SQUARED:
@@ -108,13 +108,17 @@ def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
             return True
         linear(runtime, mode, a, w, unactivated, alpha, error_flag=error_flag, name=name)
         return False
+    if gate_activation and choice in (_SKINNY, _CLUSTER):
+        # the two kernels for products in between have the SiLU gate alone: the cluster kernel's shapes go to the persistent
+        # tcgen05 kernel, the one-CTA-per-16-rows kernel's to the product on the 32-bit pipes
+        choice = _TC if choice == _CLUSTER else _SIMT
     if choice == _TC:
         ops.gemm_tc(mode, a, w, out, alpha, error_flag, label=name, act=gate_activation)
     elif choice == _STREAM:
         ops.gemm_stream(mode, a, w, out, alpha, error_flag, label=name, activation=gate_activation)
     elif choice == _SKINNY:
-        ops.gemm_skinny(mode, a, w, out, alpha, error_flag, label=name, act=gate_activation)
+        ops.gemm_skinny(mode, a, w, out, alpha, error_flag, label=name)
     elif choice == _CLUSTER:
-        ops.gemm_cluster(mode, a, w, out, alpha, error_flag, label=name, act=gate_activation)
+        ops.gemm_cluster(mode, a, w, out, alpha, error_flag, label=name)
     else:
         ops.gemm_simt(mode, a, w, out, alpha, label=name, act=gate_activation)
