@@ -34,6 +34,7 @@ __global__ void moe_route_kernel(const T* __restrict__ x, long long ld, const fl
                                  int groups, int keep, int renormalise, int* __restrict__ ids,
                                  float* __restrict__ weights, float* __restrict__ shared_gate) {
     extern __shared__ __align__(16) float route_shared[];  // x [hidden], z [experts + extra], choice scores [experts]
+    __shared__ int picked[MOE_MAX_TOP];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -107,13 +108,15 @@ __global__ void moe_route_kernel(const T* __restrict__ x, long long ld, const fl
             if (best < 0 || v > value) value = v, best = e;
         }
         if (best < 0) best = 0;                            // (fewer outputs left than `top`: the launcher refuses that)
-        ids[(size_t)t * top + c] = best;
-        weights[(size_t)t * top + c] = z[best];
+        picked[c] = best;
         chosen_sum += z[best];
         choice[best] = __int_as_float(0x7fc00000);
     }
     const float factor = renormalise ? scale / (chosen_sum + 1e-20f) : scale;
-    for (int c = 0; c < top; ++c) weights[(size_t)t * top + c] *= factor;
+    for (int c = 0; c < top; ++c) {
+        ids[(size_t)t * top + c] = picked[c];
+        weights[(size_t)t * top + c] = z[picked[c]] * factor;
+    }
     if (extra) shared_gate[t] = 1.0f / (1.0f + expf(-z[experts]));
 }
 
