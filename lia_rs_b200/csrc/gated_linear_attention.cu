@@ -7,7 +7,9 @@
 // The step's rows come from one product as [q: H d | k: H d | v: H dv | g: H dv | a: rank] in 32-bit.
 //  * `gla_encode` multiplies q by `q_scale` in place and writes L_t = log2(alpha_t) = -softplus(-z_t) / (tau ln 2) for
 //    every key channel (the small product W_a2 a_t is taken here, in 32-bit).
-//  * Single tokens (`gla_single`): one CTA per (token, head) updates the state in place and forms o from it.
+//  * Single tokens (`gla_single`): one CTA per (token, head) updates the state in place and forms o from it.  In a step of
+//    single tokens alone it also does what `gla_encode` does, for its own token and head, with the same sums in the same
+//    order: such a step has no encoding launch.
 //  * Prompt portions are cut into chunks of CHUNK tokens that run side by side, in three launches; with
 //    C_t = L_1 + ... + L_t inside the chunk (per channel, so every exponent below is <= 0 and nothing overflows):
 //      sums    U_c = sum_j diag(2^(C_len - C_j)) k_j v_j^T of each chunk, from zero, and C_len beside it;
@@ -73,12 +75,21 @@ __global__ void gla_encode_kernel(float* __restrict__ rows, long long ld, const 
     }
 }
 
+// What `gla_encode` does for a token, done by the single-token kernel itself for its own head when `w_a2` is given
+// (steps of single tokens alone then need no encoding launch): the rows are as the product left them.
+struct InlineEncode {
+    const void* w_a2;                // [heads d, rank], bfloat16 or 32-bit; null: the rows and log_decay are encoded already
+    const float* bias;               // [heads d] or null
+    int w_bf16, rank;
+    float q_scale, inv_tau;
+};
+
 template <typename TO>
 __global__ void __launch_bounds__(GLA_THREADS)
 gla_single_kernel(const float* __restrict__ rows, long long ld, const float* __restrict__ log_decay,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ single_rows,
                   const int* __restrict__ slots, const float* __restrict__ norm_weight, TO* __restrict__ out, int heads,
-                  int d, int dv, float eps) {
+                  int d, int dv, float eps, InlineEncode enc) {
     extern __shared__ float single_shared[];              // q [d], k [d], alpha [d], partial sums [max(GLA_THREADS, dv)]
     __shared__ float scratch[32];
     pdl_launch_dependents();
@@ -94,9 +105,26 @@ gla_single_kernel(const float* __restrict__ rows, long long ld, const float* __r
     float* partial = as + d;
     const float* row = rows + (size_t)t * ld;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        qs[i] = row[(size_t)h * d + i];
+        const int c = h * d + i;
         ks[i] = row[(size_t)(heads + h) * d + i];
-        as[i] = exp2f(log_decay[(size_t)t * heads * d + (size_t)h * d + i]);
+        if (enc.w_a2) {
+            // z = W_a2 a + b over r in ascending order, as the encoding kernel sums it
+            const float* a = row + (size_t)2 * heads * (d + dv);
+            float z = enc.bias ? enc.bias[c] : 0.f;
+            if (enc.w_bf16) {
+                const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(enc.w_a2) + (size_t)c * enc.rank;
+                for (int r = 0; r < enc.rank; ++r) z = fmaf(to_float(w[r]), a[r], z);
+            } else {
+                const float* w = reinterpret_cast<const float*>(enc.w_a2) + (size_t)c * enc.rank;
+                for (int r = 0; r < enc.rank; ++r) z = fmaf(w[r], a[r], z);
+            }
+            const float log_sigmoid = -(fmaxf(-z, 0.f) + log1pf(expf(-fabsf(z))));
+            as[i] = exp2f(log_sigmoid * enc.inv_tau * 1.4426950408889634f);
+            qs[i] = row[c] * enc.q_scale;
+        } else {
+            as[i] = exp2f(log_decay[(size_t)t * heads * d + c]);
+            qs[i] = row[c];
+        }
     }
     __syncthreads();
     const float* v = row + (size_t)2 * heads * d + (size_t)h * dv;
@@ -410,14 +438,27 @@ LIA_EXPORT int lia_gla_encode(float* rows, long long ld, const void* w_a2, int w
 // several tokens, `single_rows` [n_single] the batch indices of the single tokens.  rows [n, ld] 32-bit and log_decay
 // [n, heads d] as `gla_encode` left them; norm_weight [dv] 32-bit or null; state [slots, heads, d, dv] 32-bit with slot
 // stride `state_stride`; out [n, heads dv] of `out_dtype`; scratch: `lia_gla_scratch_floats(max_chunks, ...)` words.
+// With `w_a2` (a step of single tokens alone) the rows are as the product left them and `log_decay` is not read: the
+// kernel encodes each token's head itself (w_a2, bias, rank, q_scale, tau as for `lia_gla_encode`).
 LIA_EXPORT int lia_gla(const float* rows, long long ld, const float* log_decay, float* state, long long state_stride,
                        const int* segments, int n_segments, int max_chunks, const int* single_rows, int n_single,
                        const int* slots, const float* norm_weight, void* out, int out_dtype, int heads, int d, int dv,
-                       float eps, float* scratch, long long scratch_floats, cudaStream_t stream) {
+                       float eps, float* scratch, long long scratch_floats, const void* w_a2, int w_dtype, const float* bias,
+                       int rank, float q_scale, float tau, cudaStream_t stream) {
     if (heads <= 0 || d <= 0 || dv <= 0 || d > GLA_MAX || dv > GLA_MAX || ld < (long long)2 * heads * (d + dv) ||
         state_stride < (long long)heads * d * dv)
         return LIA_ERR_SIZE;
     if (out_dtype != LIA_F32 && out_dtype != LIA_BF16) return LIA_ERR_DTYPE;
+    InlineEncode enc = {};
+    if (w_a2) {
+        // the single tokens' rows are not encoded yet: only a step without portions may ask for that
+        if (n_segments > 0 || rank <= 0 || !(tau > 0.f) || ld < (long long)2 * heads * (d + dv) + rank) return LIA_ERR_SIZE;
+        if (w_dtype != LIA_F32 && w_dtype != LIA_BF16) return LIA_ERR_DTYPE;
+        enc.w_a2 = w_a2; enc.bias = bias; enc.w_bf16 = w_dtype == LIA_BF16; enc.rank = rank; enc.q_scale = q_scale;
+        enc.inv_tau = 1.0f / tau;
+    } else if (!log_decay) {
+        return LIA_ERR_SIZE;
+    }
     int code = LIA_OK;
     if (n_segments > 0) {
         if (max_chunks <= 0 || !scratch || scratch_floats < lia_gla_scratch_floats(max_chunks, heads, d, dv))
@@ -455,11 +496,11 @@ LIA_EXPORT int lia_gla(const float* rows, long long ld, const float* log_decay, 
         const size_t bytes = ((size_t)3 * d + (dv > GLA_THREADS ? dv : GLA_THREADS)) * sizeof(float);
         if (out_dtype == LIA_F32)
             code = lia_launch(gla_single_kernel<float>, dim3(n_single, heads), dim3(GLA_THREADS), bytes, stream, rows, ld,
-                              log_decay, state, state_stride, single_rows, slots, norm_weight, (float*)out, heads, d, dv, eps);
+                              log_decay, state, state_stride, single_rows, slots, norm_weight, (float*)out, heads, d, dv, eps, enc);
         else
             code = lia_launch(gla_single_kernel<__nv_bfloat16>, dim3(n_single, heads), dim3(GLA_THREADS), bytes, stream, rows,
                               ld, log_decay, state, state_stride, single_rows, slots, norm_weight, (__nv_bfloat16*)out, heads,
-                              d, dv, eps);
+                              d, dv, eps, enc);
     }
     return code;
 }

@@ -141,7 +141,8 @@ class _Signatures:
     lia_gla_encode = [c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                       c_int, c_float, c_float, c_void_p]
     lia_gla = [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_void_p, c_int,
-               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, ctypes.c_longlong, c_void_p]
+               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, ctypes.c_longlong, c_void_p, c_int,
+               c_void_p, c_int, c_float, c_float, c_void_p]
     lia_retention_chunks = [c_int, c_int]
     lia_retention_encode = [c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                             c_void_p]
@@ -1356,19 +1357,30 @@ def gla_encode(rows, w_a2, bias, log_decay, slots, heads: int, d: int, dv: int, 
 
 
 def gla(rows, log_decay, state, segments, n_segments: int, max_chunks: int, single_rows, slots, norm_weight, out, heads: int,
-        d: int, dv: int, eps: float, scratch=None):
+        d: int, dv: int, eps: float, scratch=None, encode=None):
     """S <- diag(alpha) S + k v^T, o = S^T q, out = o / rms(o) * norm_weight * silu(g) along the step's runs; rows
     [n, 2 heads (d + dv) ..] 32-bit = [q | k | v | g ..] and log_decay = log2(alpha) as `gla_encode` left them, state
-    [slots, heads, d, dv] 32-bit."""
+    [slots, heads, d, dv] 32-bit.  `encode` = (w_a2, bias, q_scale, tau), for a step of single tokens alone: the rows are as
+    the product left them, `log_decay` may be None, and the kernel does what `gla_encode` does for each token's head."""
     _cuda(log_decay, segments, single_rows, slots, norm_weight, out, scratch)
     _f32(rows, log_decay, state, norm_weight, scratch)
+    w_a2, bias, q_scale, tau = encode if encode is not None else (None, None, 1.0, 1.0)
+    if encode is not None:
+        _cuda(w_a2, bias)
+        _f32(bias)
+        if n_segments or tuple(w_a2.shape) != (heads * d, w_a2.shape[1]) or not w_a2.is_contiguous() or \
+                rows.shape[1] < 2 * heads * (d + dv) + w_a2.shape[1]:
+            raise KernelError("gla: the kernel encodes single tokens only, from rows that hold the decay's first product")
+        log_decay = None
     n_single = 0 if single_rows is None else single_rows.numel()
     if rows.stride(1) != 1 or rows.shape[1] < 2 * heads * (d + dv) or tuple(out.shape) != (rows.shape[0], heads * dv) or \
             state[0].numel() != heads * d * dv or not state[0].is_contiguous() or \
-            tuple(log_decay.shape) != (rows.shape[0], heads * d) or not log_decay.is_contiguous():
+            (log_decay is not None and (tuple(log_decay.shape) != (rows.shape[0], heads * d) or not log_decay.is_contiguous())) or \
+            (log_decay is None and encode is None):
         raise KernelError("gla: shapes do not agree")
     with _timed("gla", nbytes=rows.numel() * 4, flops=4 * rows.shape[0] * heads * d * dv):
         _check(lib().lia_gla(_p(rows), rows.stride(0), _p(log_decay), _p(state), state.stride(0), _p(segments),
                              int(n_segments), int(max_chunks), _p(single_rows), n_single, _p(slots), _p(norm_weight), _p(out),
                              dtype_code(out.dtype), heads, d, dv, float(eps), _p(scratch),
-                             0 if scratch is None else scratch.numel(), _stream()), "gla")
+                             0 if scratch is None else scratch.numel(), _p(w_a2), F32 if w_a2 is None else dtype_code(w_a2.dtype),
+                             _p(bias), 0 if w_a2 is None else w_a2.shape[1], float(q_scale), float(tau), _stream()), "gla")

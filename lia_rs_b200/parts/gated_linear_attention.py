@@ -92,12 +92,18 @@ class GatedLinearAttention(Mixer):
         flag = ctx.error_flag
         rows = ctx.buffer("gla.in", (n, self.width), torch.float32)
         linear(rt, STORE, x, self.w_in, rows, error_flag=flag, name="qkvga")
+        portions = ctx.n_prefill_segments
+        o = ctx.buffer("gla.o", (n, heads * dv), rt.compute_dtype)
+        if not portions:
+            # single tokens alone: the recurrence's kernel encodes each token's head itself
+            ops.gla(rows, None, state, ctx.prefill_segments, 0, 0, ctx.decode_rows, ctx.slots, self.norm_weight, o, heads, d, dv,
+                    self.eps, encode=(self.w_decay_up, self.decay_bias, self.q_scale, self.tau))
+            linear(rt, STORE if store else ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")
+            return
         log_decay = ctx.buffer("gla.decay", (n, heads * d), torch.float32)
         ops.gla_encode(rows, self.w_decay_up, self.decay_bias, log_decay, ctx.slots, heads, d, dv, self.q_scale, self.tau)
-        portions = ctx.n_prefill_segments
         chunks = ops.retention_chunks(n - ctx.n_single, portions) if portions else 0
         scratch = ctx.runtime.scratch("gla.chunks", ops.gla_scratch_floats(chunks, heads, d, dv), torch.float32) if chunks else None
-        o = ctx.buffer("gla.o", (n, heads * dv), rt.compute_dtype)
         ops.gla(rows, log_decay, state, ctx.prefill_segments, portions, chunks, ctx.decode_rows, ctx.slots, self.norm_weight, o,
                 heads, d, dv, self.eps, scratch=scratch)
         linear(rt, STORE if store else ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")
